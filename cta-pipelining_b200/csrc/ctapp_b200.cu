@@ -1,0 +1,519 @@
+// Host side of libctapp_b200.so: argument checking, tensor-map encoding, launches, and the small harness kernels.
+// Every entry point is extern "C" with plain pointers and sizes; see include/ctapp_b200.h.
+#include "../../include/ctapp_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+#include "reduce_sm100.cuh"
+
+using namespace ctapp;
+
+// ------------------------------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+#define CU_OK(expr)                                                                                   \
+  do {                                                                                                \
+    cudaError_t e_ = (expr);                                                                          \
+    if (e_ != cudaSuccess) return fail(static_cast<int>(e_), "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+#define ARG(cond, ...)                           \
+  do {                                           \
+    if (!(cond)) return fail(-1, __VA_ARGS__);   \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+#define GUARD(dev)   \
+  DeviceGuard g_(dev); \
+  if (!g_.ok) return fail(-2, "cannot select device %d", dev)
+
+static long long g_limit_ms = -1;
+static long long limit_ns() {
+  if (g_limit_ms < 0) {
+    const char* e = getenv("CTAPP_WAIT_LIMIT_MS");
+    g_limit_ms = e ? atoll(e) : 2000;
+    if (g_limit_ms <= 0) g_limit_ms = 2000;
+  }
+  return g_limit_ms * 1000000ll;
+}
+
+// ------------------------------------------------------------------------------------------ driver entry points
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+static void* driver_fn(const char* name) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+  return fn;
+}
+
+// bf16 row-major matrix (rows x cols, leading dimension ld elements), box box_cols x box_rows, 128-byte swizzle
+static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows) {
+  static EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(driver_fn("cuTensorMapEncodeTiled"));
+  if (!enc) return fail(-3, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(-1, "matrix base %p is not 16-byte aligned", base);
+  if ((ld * 2) % 16 != 0) return fail(-1, "leading dimension %lld is not a multiple of 8 elements", ld);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %dx%d)", (int)r, rows, cols, ld, box_cols, box_rows);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ configurations
+// Reference ids 0-9 name wgmma tiles (64|128 x 128|256).  A 64-row UMMA tile has no place here (one CTA drives a
+// 128-lane TMEM accumulator), so every id resolves to the 128-row tile with the same width.
+static int cfg_bn(int id) {
+  switch (id) {
+    case 0: case 1: case 5: case 7: return 128;
+    case 2: case 3: case 4: case 6: case 8: case 9: return 256;
+    default: return 0;
+  }
+}
+static int sm_count(int dev) {
+  static int cache[64];
+  if (dev < 0 || dev >= 64) return 0;
+  if (!cache[dev]) cudaDeviceGetAttribute(&cache[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cache[dev];
+}
+template <int BN> static int prepare_kernel() {
+  CU_OK(cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes));
+  return 0;
+}
+
+static int launch_gemm(GemmParams& p, int bn, int sms, int pdl, int dev, cudaStream_t stream) {
+  const int nsm = sm_count(dev);
+  int grid = sms > 0 ? sms : nsm;
+  if (grid > nsm) grid = nsm;
+  if (grid > p.num_tiles) grid = p.num_tiles;
+  if (grid < 1) return 0;   // nothing to do
+  p.limit_ns = limit_ns();
+  if (int r = bn == 256 ? prepare_kernel<256>() : prepare_kernel<128>()) return r;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = bn == 256 ? GemmCfg<256>::kSmemBytes : GemmCfg<128>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (bn == 256) CU_OK(cudaLaunchKernelEx(&cfg, gemm_kernel<256>, p));
+  else CU_OK(cudaLaunchKernelEx(&cfg, gemm_kernel<128>, p));
+  return 0;
+}
+
+static int fill_common(GemmParams& p, const void* A, const void* B, int M, int N, int K, int bn) {
+  memset(&p, 0, sizeof(p));
+  ARG(A && B, "null operand");
+  ARG(M > 0 && N > 0 && K > 0, "bad shape M=%d N=%d K=%d", M, N, K);
+  ARG(K % 8 == 0 && N % 8 == 0, "K=%d and N=%d must be multiples of 8", K, N);
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + bn - 1) / bn;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  if (int r = make_tmap(&p.tmA, A, M, K, K, BK, BM)) return r;
+  if (int r = make_tmap(&p.tmB, B, N, K, K, BK, bn)) return r;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ small kernels
+__global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb_len, int* ready, int ready_value) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+  for (int k = i; k < q.cap; k += stride) q.entries[k] = -1;
+  for (int k = i; k < sb_len; k += stride) sb[k] = pristine[k];
+  if (i == 0) { *q.head = 0; *q.tail = 0; }
+  if (ready) {   // single CTA: everything above is ordered before the flag
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(ready, ready_value);
+  }
+}
+
+template <int W> static int launch_reduce(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
+  tp_reduce_kernel<W, (W > 4 ? 1 : 2)><<<blocks, threads, 0, s>>>(p);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+__global__ void copy16_kernel(const int4* __restrict__ src, int4* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) dst[i] = src[i];
+}
+
+__global__ void stamp_kernel(unsigned long long* out) { *out = globaltimer(); }
+__global__ void timer_reads_kernel(unsigned long long* out, int n) { for (int i = 0; i < n; i++) out[i] = globaltimer(); }
+
+// A: t1; other = i; wait mine == i; t2.   B: wait mine == i; t; other = i.   Every wait is bounded.
+__global__ void pingpong_kernel(int* mine, int* other, unsigned long long* out, int n, int is_a, int* status, long long limit) {
+  for (int i = 1; i <= n; i++) {
+    int seen;
+    if (is_a) {
+      const unsigned long long t1 = globaltimer();
+      st_release_sys(other, i);
+      if (!spin_acquire_sys(mine, PredEq{i}, limit, seen)) { report_status(status, kStatusTimeoutProbe, i, i, seen); return; }
+      out[2 * (i - 1)] = t1; out[2 * (i - 1) + 1] = globaltimer();
+    } else {
+      if (!spin_acquire_sys(mine, PredEq{i}, limit, seen)) { report_status(status, kStatusTimeoutProbe, i, i, seen); return; }
+      out[i - 1] = globaltimer();
+      st_release_sys(other, i);
+    }
+  }
+}
+
+extern "C" {
+
+const char* ctapp_last_error(void) { return g_err; }
+int ctapp_abi_version(void) { return 1; }
+int ctapp_set_wait_limit_ms(int ms) {
+  ARG(ms > 0, "limit must be positive");
+  g_limit_ms = ms;
+  return 0;
+}
+int ctapp_get_wait_limit_ms(void) { return static_cast<int>(limit_ns() / 1000000ll); }
+
+int ctapp_config_info(int config_id, char* buf, int buf_len) {
+  const int bn = cfg_bn(config_id);
+  ARG(bn && buf && buf_len > 0, "bad config_id %d", config_id);
+  const int stages = bn == 256 ? GemmCfg<256>::kStages : GemmCfg<128>::kStages;
+  const unsigned smem = bn == 256 ? GemmCfg<256>::kSmemBytes : GemmCfg<128>::kSmemBytes;
+  snprintf(buf, buf_len, "tcgen05 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=%d", BM, bn, BK, kThreads, smem, stages, 2 * bn);
+  return 0;
+}
+int ctapp_occupancy(int config_id) { return cfg_bn(config_id) ? 1 : fail(-1, "bad config_id %d", config_id); }
+
+int ctapp_kernel_info(int which, char* buf, int buf_len) {
+  ARG(buf && buf_len > 0, "null buffer");
+  cudaFuncAttributes a;
+  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : (const void*)tp_reduce_kernel<4, 2>;
+  CU_OK(cudaFuncGetAttributes(&a, fn));
+  snprintf(buf, buf_len, "regs=%d local=%zu static_smem=%zu max_threads=%d", a.numRegs, a.localSizeBytes, a.sharedSizeBytes, a.maxThreadsPerBlock);
+  return 0;
+}
+
+int ctapp_preload(int device) {
+  GUARD(device);
+  cudaFuncAttributes a;
+  CU_OK(cudaFuncGetAttributes(&a, gemm_kernel<256>));
+  CU_OK(cudaFuncGetAttributes(&a, gemm_kernel<128>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<1, 2>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 2>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 2>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 1>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
+  CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
+  if (int r = prepare_kernel<256>()) return r;
+  if (int r = prepare_kernel<128>()) return r;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ GEMM entry points
+int ctapp_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int config_id, int group_rows, int sms, int device, void* stream) {
+  const int bn = cfg_bn(config_id);
+  ARG(bn, "bad config_id %d", config_id);
+  ARG(Y, "null output");
+  GUARD(device);
+  GemmParams p;
+  if (int r = fill_common(p, X, W, M, N, K, bn)) return r;
+  if (int r = make_tmap(&p.tmD[0], Y, M, N, N, kStoreCols, kStageRows)) return r;
+  p.mode = kModePlain;
+  p.order = kOrderGrouped;
+  p.group_rows = group_rows > 0 ? group_rows : 8;
+  return launch_gemm(p, bn, sms, 0, device, static_cast<cudaStream_t>(stream));
+}
+
+int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int config_id, const ctapp_chain_args* a, int device, void* stream) {
+  const int bn = cfg_bn(config_id);
+  ARG(bn, "bad config_id %d", config_id);
+  ARG(a && Y, "null argument");
+  GUARD(device);
+  GemmParams p;
+  if (int r = fill_common(p, X, W, M, N, K, bn)) return r;
+  ARG(a->src.entries && a->src.head && a->src.tail, "source queue pointers are required");
+  ARG(a->src.cap == p.num_tiles, "source queue capacity %d != number of tiles %d", a->src.cap, p.num_tiles);
+  ARG(a->tiles_n == p.tiles_n, "tiles_n %d does not match N=%d with tile width %d", a->tiles_n, N, bn);
+  if (a->dep_offsets) {
+    ARG(a->dep_consumers && a->scoreboard, "dep_consumers and scoreboard are required with dep_offsets");
+    ARG(a->dst.entries && a->dst.tail && a->dst.cap > 0, "downstream queue is required with dep_offsets");
+    ARG(!a->rowpanel || a->tiles_n2 > 0, "tiles_n2 is required in row-panel mode");
+  }
+  ARG(a->fence >= 0 && a->fence <= 3, "bad fence mode %d", a->fence);
+  if (int r = make_tmap(&p.tmD[0], Y, M, N, N, kStoreCols, kStageRows)) return r;
+  p.mode = kModeChain;
+  p.src = Queue{a->src.entries, a->src.head, a->src.tail, a->src.cap};
+  p.dep_offsets = a->dep_offsets; p.dep_consumers = a->dep_consumers; p.scoreboard = a->scoreboard;
+  p.dst = Queue{a->dst.entries, a->dst.head, a->dst.tail, a->dst.cap};
+  p.tiles_n2 = a->tiles_n2; p.rowpanel = a->rowpanel; p.skip_wait = a->skip_wait;
+  p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
+  p.status = a->status; p.stamps = a->stamps;
+  return launch_gemm(p, bn, a->sms, 0, device, static_cast<cudaStream_t>(stream));
+}
+
+int ctapp_chain_reset(ctapp_queue q, int* scoreboard, const int* pristine, int sb_len, int* ready_flag, int ready_value, int device, void* stream) {
+  ARG(q.entries && q.head && q.tail && q.cap > 0, "bad queue");
+  ARG(sb_len == 0 || (scoreboard && pristine), "scoreboard pointers are required when scoreboard_len > 0");
+  GUARD(device);
+  chain_reset_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(Queue{q.entries, q.head, q.tail, q.cap}, scoreboard, pristine, sb_len, ready_flag, ready_value);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ tensor-parallel boundary
+int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
+  ARG(a, "null args");
+  ARG(a->mode == 0 || a->mode == 7, "tp_down mode %d is not supported (0 | 7)", a->mode);
+  ARG(a->world >= 1 && a->world <= CTAPP_MAX_WORLD && a->rank >= 0 && a->rank < a->world, "bad rank %d / world %d", a->rank, a->world);
+  GUARD(device);
+  GemmParams p;
+  if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, 256)) return r;
+  ARG(a->N % 256 == 0, "N=%d must be a multiple of 256", a->N);
+  p.status = a->status; p.stamps = a->trace;
+  p.pdl_trigger = a->pdl_trigger; p.pdl_wait = a->pdl;
+  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
+  if (a->raster == 2) p.order = kOrderNFast;
+  else {
+    ARG(a->tail_cols >= 0 && a->tail_cols <= p.tiles_n, "bad tail_cols %d", a->tail_cols);
+    p.order = kOrderMFastTail; p.tail_cols = a->tail_cols;
+  }
+  if (a->mode == 0) {
+    ARG(a->D, "mode 0 needs D");
+    if (int r = make_tmap(&p.tmD[0], a->D, a->M, a->N, a->N, kStoreCols, kStageRows)) return r;
+    p.mode = kModePlain;
+  } else {
+    ARG(a->M % 128 == 0, "mode 7 needs M %% 128 == 0 (M=%d)", a->M);
+    ARG(a->dst_rows >= ((a->M / 128 + a->world - 1) / a->world) * 128 && a->panels_per_owner * 128 <= a->dst_rows,
+        "inbox slot of %d rows / %d panels per owner is too small for M=%d on %d ranks", a->dst_rows, a->panels_per_owner, a->M, a->world);
+    p.mode = kModeTpProducer;
+    p.world = a->world; p.rank = a->rank; p.ppo = a->panels_per_owner;
+    for (int d = 0; d < a->world; d++) {
+      ARG(a->dst_ptrs[d] && a->peer_tile_flags[d], "missing destination %d", d);
+      if (int r = make_tmap(&p.tmD[d], a->dst_ptrs[d], a->dst_rows, a->N, a->N, kStoreCols, kStageRows)) return r;
+      p.peer_tile_flags[d] = a->peer_tile_flags[d];
+    }
+  }
+  return launch_gemm(p, 256, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
+}
+
+int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
+  ARG(a, "null args");
+  ARG(a->mode == 0 || a->mode == 5, "tp_qkv mode %d is not supported (0 | 5)", a->mode);
+  ARG(a->tile == 256 || a->tile == 128 || a->tile == 0, "bad tile %d", a->tile);
+  const int bn = a->tile == 128 ? 128 : 256;
+  GUARD(device);
+  GemmParams p;
+  if (int r = fill_common(p, a->X, a->W, a->M, a->N, a->K, bn)) return r;
+  ARG(a->Y, "null output");
+  if (int r = make_tmap(&p.tmD[0], a->Y, a->M, a->N, a->N, kStoreCols, kStageRows)) return r;
+  p.status = a->status; p.stamps = a->trace;
+  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
+  p.order = a->raster == 2 ? kOrderNFast : kOrderMFastTail;
+  p.tail_cols = 0;
+  p.rowss = a->rowss; p.inv_k = 1.0f / static_cast<float>(a->K); p.eps = a->eps;
+  if (a->mode == 5) {
+    ARG(a->panel_flag, "mode 5 needs panel_flag");
+    p.mode = kModeTpConsumer; p.panel_flag = a->panel_flag;
+    p.pdl_wait = 0;            // the per-panel flags carry the dependency on the producer grid
+  } else {
+    p.mode = a->rowss ? kModeTpConsumer : kModePlain;   // mode 0 with rowss: scale only, no waits
+    p.panel_flag = nullptr;
+    p.pdl_wait = a->pdl;
+  }
+  return launch_gemm(p, bn, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
+}
+
+int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
+  ARG(a, "null args");
+  ARG(a->world == 1 || a->world == 2 || a->world == 4 || a->world == 8, "world %d is not supported (1 | 2 | 4 | 8)", a->world);
+  ARG(a->rank >= 0 && a->rank < a->world, "bad rank %d", a->rank);
+  ARG(a->M >= 0 && a->M % 128 == 0 && a->n1 > 0 && a->n1 % 256 == 0, "bad shape M=%d n1=%d", a->M, a->n1);
+  ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
+  ARG(a->tile_flags && a->rowss_local && a->panel_done, "null protocol buffer");
+  ARG(a->tail_cols >= 0 && a->tail_cols <= a->n1 / 256, "bad tail_cols %d", a->tail_cols);
+  GUARD(device);
+  ReduceParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.n1 = a->n1; p.rank = a->rank; p.world = a->world;
+  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
+  p.tile_flags = a->tile_flags;
+  for (int d = 0; d < a->world; d++) {
+    ARG(a->inbox[d] && a->peer_x[d] && a->peer_rowss[d] && a->peer_panel_flag[d], "missing peer buffer %d", d);
+    p.inbox[d] = static_cast<const uint4*>(a->inbox[d]);
+    p.x[d] = static_cast<uint4*>(a->peer_x[d]);
+    p.rowss[d] = a->peer_rowss[d];
+    p.panel_flag[d] = a->peer_panel_flag[d];
+  }
+  p.resid = static_cast<const uint4*>(a->resid);
+  p.rowss_local = a->rowss_local; p.panel_done = a->panel_done;
+  p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
+  p.unit_ctr = a->unit_ctr; p.trace = a->trace; p.status = a->status;
+  p.limit_ns = limit_ns();
+  if (a->M == 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (a->world) {
+    case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
+    case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);
+    case 4: return launch_reduce<4>(p, a->blocks, a->threads, s);
+    default: return launch_reduce<8>(p, a->blocks, a->threads, s);
+  }
+}
+
+int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream) {
+  ARG(epoch_dev && rowss_local && panel_done && M >= 0 && M % 128 == 0, "bad arguments");
+  GUARD(device);
+  int blocks = (M / 4 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 64) blocks = 64;
+  tp_step_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(epoch_dev, reinterpret_cast<float4*>(rowss_local), panel_done, M, role_ctr);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+int ctapp_add_rmsnorm(const void* a, const void* resid, const void* gamma, void* x_out, void* y_out, int M, int n1, float eps, int device, void* stream) {
+  ARG(a && gamma && y_out && M > 0 && n1 > 0 && n1 % 8 == 0 && n1 <= 16384, "bad arguments");
+  GUARD(device);
+  add_rmsnorm_kernel<<<M, 256, n1 * 2, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(resid), static_cast<const uint4*>(gamma),
+                                                                           static_cast<uint4*>(x_out), static_cast<uint4*>(y_out), n1, eps);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ harness natives
+int ctapp_enable_peer_access(int device, int peer) {
+  GUARD(device);
+  int can = 0;
+  CU_OK(cudaDeviceCanAccessPeer(&can, device, peer));
+  ARG(can, "device %d cannot access device %d", device, peer);
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return 0; }
+  CU_OK(e);
+  return 0;
+}
+
+static volatile int* g_gate = nullptr;
+static CUdeviceptr g_gate_dev = 0;
+int ctapp_gate_alloc(void) {
+  if (g_gate) return 0;
+  void *h, *d;
+  CU_OK(cudaHostAlloc(&h, sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped));
+  CU_OK(cudaHostGetDevicePointer(&d, h, 0));
+  g_gate = static_cast<volatile int*>(h);
+  g_gate_dev = reinterpret_cast<CUdeviceptr>(d);
+  *g_gate = 0;
+  return 0;
+}
+int ctapp_gate_set(int value) {
+  ARG(g_gate, "gate_alloc has not been called");
+  *g_gate = value;
+  return 0;
+}
+int ctapp_gate_wait(int device, void* stream) {
+  ARG(g_gate, "gate_alloc has not been called");
+  static StreamWaitValue32Fn fn = reinterpret_cast<StreamWaitValue32Fn>(driver_fn("cuStreamWaitValue32"));
+  ARG(fn, "cuStreamWaitValue32 is not available from this driver");
+  GUARD(device);
+  CUresult r = fn(static_cast<CUstream>(stream), g_gate_dev, 1, CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) return fail(-3, "cuStreamWaitValue32 failed with %d", (int)r);
+  return 0;
+}
+int ctapp_peer_copy(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream) {
+  GUARD(src_device);
+  CU_OK(cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+int ctapp_p2p_store_bw(const void* src, void* dst, size_t bytes, int device, void* stream) {
+  ARG(src && dst && bytes % 16 == 0, "bad arguments");
+  GUARD(device);
+  copy16_kernel<<<sm_count(device) * 8, 512, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int4*>(src), static_cast<int4*>(dst), bytes / 16);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+int ctapp_stamp_now(unsigned long long* out, int device, void* stream) {
+  GUARD(device);
+  stamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(out);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_timer_reads(unsigned long long* out, int n, int device, void* stream) {
+  GUARD(device);
+  timer_reads_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(out, n);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+int ctapp_pingpong(int* mine, int* other, unsigned long long* out, int n, int is_a, int* status, int device, void* stream) {
+  ARG(mine && other && out && n > 0, "bad arguments");
+  GUARD(device);
+  pingpong_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(mine, other, out, n, is_a, status, limit_ns());
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+int ctapp_malloc(void** out, size_t bytes, int device) {
+  ARG(out && bytes > 0, "bad arguments");
+  GUARD(device);
+  CU_OK(cudaMalloc(out, bytes));
+  return 0;
+}
+int ctapp_free(void* ptr, int device) {
+  GUARD(device);
+  CU_OK(cudaFree(ptr));
+  return 0;
+}
+int ctapp_ipc_get_handle(void* ptr, unsigned char handle64[64], int device) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  GUARD(device);
+  cudaIpcMemHandle_t h;
+  CU_OK(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+int ctapp_ipc_open(const unsigned char handle64[64], void** out, int device) {
+  GUARD(device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  CU_OK(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+int ctapp_ipc_close(void* ptr, int device) {
+  GUARD(device);
+  CU_OK(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,179 @@
+"""Layer-per-GPU GEMM chain with CTA-level pipelining (mirrors reference ctapp/pipeline.py).
+
+``build_deps`` builds the dependency CSR and the scoreboard; ``Pipeline`` is the reference's 2-GPU, 2-layer object with
+the same constructor, attributes and methods; ``Chain`` generalises it to any number of stages driven from one
+process; ``ChainStage`` is one stage owned by one process (one process per GPU), wired to its neighbours through
+IPC-mapped buffers.
+"""
+from __future__ import annotations
+
+import torch
+
+from ctapp.ext import check_status, load, new_status
+
+EMPTY = -1
+
+
+def build_deps(M, N1, N2, BM1, BN1, BM2, BN2, rowpanel=True):
+    """CSR dependency array over producer tiles (row-major ids m1 * tn1 + n1) and the consumer scoreboard's initial
+    values, as int32 CPU tensors ``(dep_offsets, dep_consumers, init)``.
+
+    rowpanel=True: one counter per consumer row panel, stored 32 ints apart (one 128-byte line each); the consumers of a
+    producer tile are the row panels its rows intersect.  rowpanel=False: one counter per consumer tile (m2 * tn2 + n2).
+    Same results as reference ctapp/pipeline.py:7-31.
+    """
+    tm1, tn1 = -(-M // BM1), -(-N1 // BN1)
+    tm2, tn2 = -(-M // BM2), -(-N2 // BN2)
+    m1 = torch.arange(tm1, dtype=torch.int64)
+    first = m1 * BM1
+    last = torch.minimum((m1 + 1) * BM1, torch.tensor(M)) - 1
+    lo, hi = first // BM2, last // BM2
+    width = 1 if rowpanel else tn2
+    per_tile = ((hi - lo + 1) * width).repeat_interleave(tn1)           # out-degree of every producer tile
+    offsets = torch.zeros(tm1 * tn1 + 1, dtype=torch.int64)
+    torch.cumsum(per_tile, 0, out=offsets[1:])
+    nnz = int(offsets[-1])
+    owner = torch.repeat_interleave(torch.arange(tm1 * tn1), per_tile)  # producer tile of every CSR slot
+    k = torch.arange(nnz) - offsets[owner]                              # position inside the tile's CSR row
+    panel = lo[owner // tn1] + k // width
+    consumers = panel if rowpanel else panel * tn2 + k % width
+    counts = torch.bincount(consumers, minlength=tm2 if rowpanel else tm2 * tn2)
+    if rowpanel:
+        init = torch.zeros(tm2 * 32, dtype=torch.int64)
+        init[::32] = counts
+    else:
+        init = counts
+    return offsets.int(), consumers.int(), init.int()
+
+
+def producer_order(P, tn1, group_rows):
+    """Tile ids in the order the first stage works through them: groups of ``group_rows`` tile rows, n-major inside a
+    group (reference ctapp/pipeline.py:48-51).  group_rows == 0 is ascending ids."""
+    if not group_rows:
+        return torch.arange(P, dtype=torch.int32)
+    t = torch.arange(P)
+    m, n = t // tn1, t % tn1
+    return torch.argsort(((m // group_rows) * tn1 + n) * group_rows + m % group_rows, stable=True).int()
+
+
+def _tile(ext, cfg):
+    s = ext.config_info(cfg).split("tile ")[1].split("x")
+    return int(s[0]), int(s[1])
+
+
+class Pipeline:
+    """2-layer CTA-pipelined run: the producer GEMM on devA stores Y1 into devB's memory tile by tile, the consumer GEMM
+    on devB starts each tile as soon as the row panel it reads is complete.  Same constructor, attributes and methods
+    as reference ctapp/pipeline.py:34-81; a two-stage ``Chain`` underneath.  devA == devB runs both stages on one GPU,
+    one after the other on the same stream."""
+
+    def __init__(self, M, K, N1, N2, cfg1, cfg2, devA=0, devB=1, skip_wait=0, fence=0, group_rows=0, scoreboard="rowpanel"):
+        assert scoreboard in ("rowpanel", "tile")
+        ch = Chain(M, K, [N1, N2], [devA, devB], cfg=[cfg1, cfg2], group_rows=group_rows, scoreboard=scoreboard,
+                   fence=fence, skip_wait=skip_wait)
+        self.chain, self.ext = ch, ch.ext
+        self.M, self.cfg1, self.cfg2, self.skip_wait, self.fence, self.rowpanel = M, cfg1, cfg2, skip_wait, fence, ch.rowpanel
+        self.a, self.b = ch.devs
+        self.tn1, self.tn2 = ch.tn
+        self.src_a, self.src_b = ch.entries
+        self.head_a, self.head_b = ch.head
+        self.tail_a, self.tail_b = ch.tail
+        self.dep_off, self.dep_cons, self.sb, self.sb_pristine = ch.dep_off[0], ch.dep_cons[0], ch.sb[0], ch.sb_pristine[0]
+        self.Y1, self.Y2 = ch.Y
+        self.status_a, self.status_b = ch.status
+
+    def tile(self, cfg):
+        return _tile(self.ext, cfg)
+
+    def reset(self):
+        self.chain.reset()
+
+    def run(self, X, W1, W2):
+        return self.chain.run(X, [W1, W2])
+
+    def check(self):
+        """Synchronise both devices and raise if a device-side wait gave up."""
+        self.chain.check()
+
+
+class Chain:
+    """N-stage chain driven from one process: stage g runs on ``devices[g]`` with weight W_g (N_g, N_{g-1}); its output
+    tiles land in the memory of ``devices[g+1]`` and are announced in that GPU's work queue.  Repeated devices are
+    allowed (stages then run back to back on that GPU's stream)."""
+
+    def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0):
+        self.ext = load()
+        self.sms = sms
+        self.M, self.K, self.widths, self.fence, self.skip_wait = M, K, list(widths), fence, skip_wait
+        self.cfg = list(cfg) if isinstance(cfg, (list, tuple)) else [cfg] * len(self.widths)
+        self.devs = [torch.device("cuda", d) for d in devices]
+        assert len(self.devs) == len(self.widths) >= 1
+        self.rowpanel = int(scoreboard == "rowpanel")
+        for a, b in zip(devices[:-1], devices[1:]):
+            if a != b:
+                self.ext.enable_peer_access(a, b); self.ext.enable_peer_access(b, a)
+        for d in set(devices):
+            self.ext.preload(d)
+        tiles = [_tile(self.ext, c) for c in self.cfg]
+        i32 = dict(dtype=torch.int32)
+        L = len(self.widths)
+        self.tn = [-(-n // t[1]) for n, t in zip(self.widths, tiles)]
+        self.ntiles = [-(-M // t[0]) * tn for t, tn in zip(tiles, self.tn)]
+        self.entries, self.head, self.tail, self.Y, self.status = [], [], [], [], []
+        self.dep_off, self.dep_cons, self.sb, self.sb_pristine = [], [], [], []
+        for g in range(L):
+            dev = self.devs[g]
+            if g == 0:
+                self.entries.append(producer_order(self.ntiles[0], self.tn[0], group_rows).to(dev))
+                self.tail.append(torch.full((1,), self.ntiles[0], device=dev, **i32))
+            else:
+                self.entries.append(torch.full((self.ntiles[g],), EMPTY, device=dev, **i32))
+                self.tail.append(torch.zeros(1, device=dev, **i32))
+            self.head.append(torch.zeros(1, device=dev, **i32))
+            self.status.append(new_status(dev))
+            out_dev = self.devs[g + 1] if g + 1 < L else dev
+            self.Y.append(torch.empty(M, self.widths[g], device=out_dev, dtype=torch.bfloat16))
+            if g + 1 < L:
+                off, cons, sb = build_deps(M, self.widths[g], self.widths[g + 1], *tiles[g], *tiles[g + 1], bool(self.rowpanel))
+                self.dep_off.append(off.to(dev)); self.dep_cons.append(cons.to(dev))
+                self.sb_pristine.append(sb.to(dev)); self.sb.append(sb.to(dev).clone())
+            else:
+                self.dep_off.append(None); self.dep_cons.append(None); self.sb.append(None); self.sb_pristine.append(None)
+
+    def reset(self):
+        L = len(self.widths)
+        evs = [None] * L
+        for g in range(L):
+            with torch.cuda.device(self.devs[g]):
+                self.head[g].zero_()
+                if g > 0:
+                    self.entries[g].fill_(EMPTY); self.tail[g].zero_()
+                if self.sb[g] is not None:
+                    self.sb[g].copy_(self.sb_pristine[g])
+                evs[g] = torch.cuda.Event(); evs[g].record()
+        for g in range(L - 1):   # stage g may write into stage g+1's memory only after that stage's reset
+            if self.devs[g] != self.devs[g + 1]:
+                torch.cuda.current_stream(self.devs[g]).wait_event(evs[g + 1])
+
+    def enqueue(self, X, Ws):
+        L = len(self.widths)
+        for g in range(L):
+            with torch.cuda.device(self.devs[g]):
+                inp = X if g == 0 else self.Y[g - 1]
+                last = g + 1 == L
+                self.ext.ctapp_gemm(inp, Ws[g], self.Y[g], self.cfg[g], self.entries[g], self.head[g], self.tail[g],
+                                    self.dep_off[g], self.dep_cons[g], self.sb[g],
+                                    None if last else self.entries[g + 1], None if last else self.head[g + 1],
+                                    None if last else self.tail[g + 1], self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
+                                    tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms)
+        return self.Y[-1]
+
+    def run(self, X, Ws):
+        self.reset()
+        return self.enqueue(X, Ws)
+
+    def check(self):
+        for d in self.devs:
+            torch.cuda.synchronize(d)
+        for g, s in enumerate(self.status):
+            check_status(s, f"chain stage {g}")

@@ -1,0 +1,161 @@
+/* C ABI of the B200-native CTA-pipelining library (libctapp_b200.so).
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is a CUDA device address valid on the GPU `device`
+ * (peer addresses are device addresses of another GPU made reachable by peer access or an IPC mapping).  Work is
+ * enqueued on `stream` (a cudaStream_t, may be NULL for the legacy default stream) of GPU `device`; the call
+ * returns as soon as the work is enqueued.  Return value: 0 = ok, negative = argument error, positive = CUDA error
+ * code; ctapp_last_error() gives the text.  Device-side waits are bounded: a wait that gives up writes a code into
+ * the caller's `status` buffer (CTAPP_STATUS_INTS ints, zeroed by the caller) and the kernel drains and exits.
+ *
+ * Each entry point names the reference binding it replaces (file:line inside the reference project).
+ */
+#ifndef CTAPP_B200_H
+#define CTAPP_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CTAPP_STATUS_INTS 8
+#define CTAPP_MAX_WORLD 8
+
+/* ---- library ---- */
+const char* ctapp_last_error(void);
+int ctapp_abi_version(void);
+/* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
+int ctapp_set_wait_limit_ms(int ms);
+int ctapp_get_wait_limit_ms(void);
+/* Loads every kernel of the library on `device` (no launch), so that no lazy module load can happen while a
+ * kernel that waits on a peer is resident.  Replaces the warm-up launches of ctapp/tp4.py:240-260. */
+int ctapp_preload(int device);
+
+/* ---- harness natives (csrc/gemm_tma.cu:167-248) ---- */
+int ctapp_enable_peer_access(int device, int peer);                                     /* gemm_tma.cu:167-172 */
+int ctapp_gate_alloc(void);                                                             /* gemm_tma.cu:192-197 */
+int ctapp_gate_set(int value);                                                          /* gemm_tma.cu:198 */
+int ctapp_gate_wait(int device, void* stream);                                          /* gemm_tma.cu:200-203 */
+int ctapp_peer_copy(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream);   /* gemm_tma.cu:205-208 */
+int ctapp_p2p_store_bw(const void* src, void* dst, size_t bytes, int device, void* stream);                    /* gemm_tma.cu:174-186 */
+int ctapp_stamp_now(unsigned long long* out, int device, void* stream);                 /* gemm_tma.cu:214-218 */
+int ctapp_timer_reads(unsigned long long* out, int n, int device, void* stream);        /* gemm_tma.cu:221-225 */
+/* Bounded ping-pong between two GPUs; status may be NULL. */                            /* gemm_tma.cu:229-248 */
+int ctapp_pingpong(int* mine, int* other, unsigned long long* out, int n, int is_a, int* status, int device, void* stream);
+/* Cross-process mapping of device memory allocated by this library (one process per GPU). */
+int ctapp_malloc(void** out, size_t bytes, int device);
+int ctapp_free(void* ptr, int device);
+int ctapp_ipc_get_handle(void* ptr, unsigned char handle64[64], int device);
+int ctapp_ipc_open(const unsigned char handle64[64], void** out, int device);
+int ctapp_ipc_close(void* ptr, int device);
+
+/* ---- GEMM configurations (csrc/gemm_tma.cu:116-126, 155-165) ---- */
+int ctapp_config_info(int config_id, char* buf, int buf_len);   /* text contains "tile BMxBNxBK" */
+int ctapp_occupancy(int config_id);                              /* resident CTAs per SM */
+
+/* Y[M,N] = X[M,K] * W[N,K]^T, bf16 in, fp32 accumulate, bf16 out.  gemm_tma.cu:128-134 (gemm_tma), gemm_coop.cu:101-114
+ * (coop_gemm).  group_rows: tile rows walked together (0 = library default); sms: CTAs to launch (0 = all SMs). */
+int ctapp_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int config_id, int group_rows, int sms,
+               int device, void* stream);
+
+/* ---- layer-per-GPU chain (csrc/ctapp.cuh:5-69, csrc/gemm_tma.cu:136-153) ---- */
+typedef struct ctapp_queue {   /* ctapp.cuh:5 */
+  int* entries;                /* cap ints, -1 = empty */
+  int* head;
+  int* tail;
+  int cap;
+} ctapp_queue;
+
+typedef struct ctapp_chain_args {     /* ctapp.cuh:7-19 */
+  unsigned long long* stamps;         /* NULL = off; else 8 u64 per CTA */
+  ctapp_queue src;                    /* this GPU's work queue; cap == number of tiles of this GEMM */
+  const int* dep_offsets;             /* CSR over this GEMM's tiles, NULL for the last stage */
+  const int* dep_consumers;
+  int* scoreboard;                    /* local counters, one per downstream tile or row panel (stride 32 ints) */
+  ctapp_queue dst;                    /* the downstream GPU's queue (peer addresses) */
+  int tiles_n;                        /* n-tiles of this GEMM */
+  int skip_wait;                      /* negative control: take tile = pop index without waiting */
+  int fence;                          /* accepted for compatibility; the TMA-store epilogue always orders as mode 1 */
+  int tiles_n2;                       /* n-tiles of the downstream GEMM (row-panel mode) */
+  int rowpanel;
+  const int* dst_ready;               /* optional local flag the downstream GPU raises to `ready_value` once it has
+                                         reset its queue; NULL = the caller orders the reset with stream events */
+  int ready_value;
+  int* status;                        /* CTAPP_STATUS_INTS ints or NULL */
+  int sms;                            /* CTAs to launch, 0 = all SMs */
+} ctapp_chain_args;
+
+/* One stage of the chain: Y = X * W^T with tile ids popped from args->src and completion published into args->dst.
+ * Y may be a peer address (the next GPU's input).  gemm_tma.cu:136-153 (ctapp_gemm). */
+int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int config_id,
+                     const ctapp_chain_args* args, int device, void* stream);
+/* Reset a stage's queue for the next run (entries = -1, head = tail = 0, scoreboard = pristine) and then, if
+ * ready_flag != NULL, release ready_flag[0] = ready_value at system scope (a flag in the upstream GPU's memory).
+ * ctapp/pipeline.py:64-71 (Pipeline.reset), as one kernel. */
+int ctapp_chain_reset(ctapp_queue q, int* scoreboard, const int* scoreboard_pristine, int scoreboard_len,
+                      int* ready_flag, int ready_value, int device, void* stream);
+
+/* ---- tensor-parallel layer boundary (csrc/ctapp_tp4.cuh, csrc/gemm_tp4.cu) ---- */
+typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0 and 7 */
+  const void* A; const void* W; void* D;   /* A (M,K), W (N,K); D (M,N) used in mode 0 only */
+  int M, N, K;
+  int raster, swizzle, mode, rank, world;
+  int epoch; const int* epoch_dev;         /* epoch_dev != NULL overrides epoch */
+  void* dst_ptrs[CTAPP_MAX_WORLD];         /* mode 7: this rank's inbox slot at every owner, (dst_rows, N) bf16 */
+  int dst_rows;
+  int* peer_tile_flags[CTAPP_MAX_WORLD];   /* mode 7: every owner's tile_flags[world][ppo][N/256] */
+  int panels_per_owner;
+  int sms, pdl_trigger, pdl, tail_cols;
+  unsigned long long* trace;
+  int* status;
+} ctapp_tp_down_args;
+int ctapp_tp_down(const ctapp_tp_down_args* args, int device, void* stream);
+
+typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 and 5 */
+  const void* X; const void* W; void* Y;   /* X (M,K) local, written by the owner reducers; W (N,K) gamma-folded; Y (M,N) */
+  int M, N, K;
+  int raster, swizzle, mode;
+  int epoch; const int* epoch_dev;
+  const int* panel_flag;                   /* [M/128], value flags */
+  const float* rowss;                      /* [M] row sums of squares of X; NULL = no scaling */
+  float eps;
+  int sms, pdl, tile;                      /* tile: 256 | 128 */
+  unsigned long long* trace;
+  int* status;
+} ctapp_tp_qkv_args;
+int ctapp_tp_qkv(const ctapp_tp_qkv_args* args, int device, void* stream);
+
+typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, version 5 variant 1) */
+  int M, n1, rank, world;
+  int epoch; const int* epoch_dev;
+  int blocks, threads;
+  const int* tile_flags;                    /* local [world][ppo][n1/256] */
+  const void* inbox[CTAPP_MAX_WORLD];       /* local inbox slot of every source rank */
+  const void* resid;                        /* (M, n1) bf16 or NULL */
+  void* peer_x[CTAPP_MAX_WORLD];            /* x buffer of every rank, (M, n1) bf16 */
+  float* peer_rowss[CTAPP_MAX_WORLD];       /* rowss buffer of every rank, [M] */
+  int* peer_panel_flag[CTAPP_MAX_WORLD];    /* panel_flag of every rank, [M/128] */
+  float* rowss_local;                       /* [M] accumulators, zeroed by ctapp_tp_step */
+  int* panel_done;                          /* [M/128] arrival counters, zeroed by ctapp_tp_step */
+  int panels_per_owner, tail_cols;
+  int* unit_ctr;                            /* NULL = static unit assignment */
+  unsigned long long* trace;
+  int* status;
+} ctapp_tp_reduce_args;
+int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
+
+/* epoch_dev[0] += 1; zero rowss_local[0:M], panel_done[0:M/128] and role_ctr[0:2].  gemm_tp4.cu:362-372 (tp4_step). */
+int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream);
+
+/* Comparison baseline only: x = a + resid (bf16), y = rmsnorm(x) * gamma, one pass (the fused add+RMSNorm a serving
+ * stack runs after an all-reduce).  No counterpart in the reference (it used eager torch, ctapp/tp4.py:47-50). */
+int ctapp_add_rmsnorm(const void* a, const void* resid, const void* gamma, void* x_out, void* y_out, int M, int n1,
+                      float eps, int device, void* stream);
+
+/* registers / shared memory / spill of a kernel: which = 0 GEMM 128x256, 1 GEMM 128x128, 2 reducer.  gemm_tp4.cu:374-390 */
+int ctapp_kernel_info(int which, char* buf, int buf_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTAPP_B200_H */

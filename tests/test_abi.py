@@ -1,0 +1,58 @@
+"""The C-ABI shared library builds, loads without a GPU, and exports every symbol the public header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "ctapp_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ctapp_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_exports_header_symbols():
+    from ctapp import ext
+    path = ext.build()
+    assert os.path.exists(path)
+    lib = ctypes.CDLL(path)
+    syms = header_symbols()
+    assert len(syms) >= 25
+    for s in syms:
+        assert hasattr(lib, s), f"{s} is declared in include/ctapp_b200.h but not exported"
+    # the binding table covers the header, and nothing else
+    assert sorted(ext.EXPORTS) == syms
+
+
+def test_argument_errors_without_gpu():
+    """Calls that fail in argument checking never touch CUDA, so they can run here."""
+    from ctapp import ext
+    lib = ext.lib()
+    assert lib.ctapp_abi_version() == 1
+    buf = ctypes.create_string_buffer(256)
+    assert lib.ctapp_config_info(3, buf, 256) == 0 and b"tile 128x256x64" in buf.value
+    assert lib.ctapp_config_info(5, buf, 256) == 0 and b"tile 128x128x64" in buf.value
+    assert lib.ctapp_config_info(77, buf, 256) < 0 and b"bad config_id" in lib.ctapp_last_error()
+    assert lib.ctapp_occupancy(3) == 1
+    assert lib.ctapp_set_wait_limit_ms(0) < 0
+    assert lib.ctapp_set_wait_limit_ms(1500) == 0 and lib.ctapp_get_wait_limit_ms() == 1500
+    assert lib.ctapp_set_wait_limit_ms(2000) == 0
+    assert lib.ctapp_gemm(None, None, None, 128, 128, 128, 42, 0, 0, 0, None) < 0
+    assert lib.ctapp_gate_set(1) < 0 and b"gate_alloc" in lib.ctapp_last_error()
+
+
+def test_python_module_surface():
+    """The two module objects carry the function names of the reference's extension modules."""
+    from ctapp import ext
+    m1, m2 = ext.load(), ext.load_tp4()
+    for name in ("gemm_tma", "ctapp_gemm", "coop_gemm", "coop_info", "config_info", "occupancy", "enable_peer_access",
+                 "p2p_store_bw_kernel", "gate_alloc", "gate_set", "gate_wait", "peer_copy", "stamp_now", "timer_reads", "pingpong"):
+        assert callable(getattr(m1, name)), name
+    for name in ("tp4_down", "tp4_qkv", "tp4_reduce", "tp4_step", "tp4_info", "tp4_set_debug"):
+        assert callable(getattr(m2, name)), name
+    assert "tile 128x256x64" in m1.config_info(3)
+    with pytest.raises(RuntimeError):
+        m1.config_info(99)

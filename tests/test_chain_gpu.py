@@ -1,0 +1,146 @@
+"""The chain protocol on one GPU (both stages on the same device, one after the other on one stream) and, when two GPUs are
+present, as a real producer/consumer pair.  Values are checked against the CPU oracle; queue order and scoreboard counts are
+checked bit-exactly: against the sequential protocol model when the producer runs as a single CTA (its publish order is then
+deterministic), and through order-independent invariants under full concurrency."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import chain as oc
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_case(M, K, N1, N2, cfg1, cfg2, devA, devB, runs=3, **kw):
+    from ctapp.pipeline import Pipeline
+    pl = Pipeline(M, K, N1, N2, cfg1, cfg2, devA=devA, devB=devB, **kw)
+    X, (W1, W2) = oc.make_chain_inputs(M, K, [N1, N2], seed=0)
+    Xa, W1a, W2b = X.to(pl.a), W1.to(pl.a), W2.to(pl.b)
+    # the same kernels run without the protocol, one after the other
+    Y1s = torch.empty(M, N1, dtype=torch.bfloat16, device=pl.a)
+    pl.ext.gemm_tma(Xa, W1a, Y1s, cfg1)
+    Y1s_b = Y1s.to(pl.b)
+    Y2s = torch.empty(M, N2, dtype=torch.bfloat16, device=pl.b)
+    with torch.cuda.device(pl.b):
+        pl.ext.gemm_tma(Y1s_b, W2b, Y2s, cfg2)
+    torch.cuda.synchronize(pl.a); torch.cuda.synchronize(pl.b)
+    for r in range(runs):
+        with torch.cuda.device(pl.b):
+            pl.Y1.fill_(float("nan")); pl.Y2.fill_(float("nan"))
+        torch.cuda.synchronize(pl.b)
+        pl.run(Xa, W1a, W2b)
+        pl.check()
+        assert torch.equal(pl.Y1, Y1s_b), f"run {r}: pipelined Y1 differs from the sequential run in {(pl.Y1 != Y1s_b).sum().item()} elements"
+        assert torch.equal(pl.Y2, Y2s), f"run {r}: pipelined Y2 differs from the sequential run in {(pl.Y2 != Y2s).sum().item()} elements"
+        BM2, BN2 = pl.tile(cfg2)
+        C = -(-M // BM2) * pl.tn2
+        bad = oc.check_link_invariants(pl.src_b.cpu().numpy(), int(pl.tail_b.item()), pl.sb.cpu().numpy(), C, pl.tn2, bool(pl.rowpanel))
+        assert bad == [], bad
+        assert int(pl.head_a.item()) >= pl.src_a.numel() and int(pl.head_b.item()) >= C
+    return pl, X, W1, W2
+
+
+@pytest.mark.parametrize("case", [(256, 512, 512, 768, 3, 3, {}), (512, 1024, 1024, 1024, 5, 3, dict(group_rows=2)),
+                                  (384, 512, 768, 512, 3, 5, dict(scoreboard="tile")), (1000, 520, 1000, 264, 5, 5, dict(group_rows=8))])
+def test_chain_one_gpu_small(case):
+    M, K, N1, N2, c1, c2, kw = case
+    pl, X, W1, W2 = _run_case(M, K, N1, N2, c1, c2, 0, 0, **kw)
+    ref = oc.chain_reference(X, [W1, W2])
+    mx, mean = oc.error_stats(pl.Y2.cpu(), ref)
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+def test_chain_one_gpu_headline_config_vs_oracle():
+    """M=1024, N=K=8192 (the CPU-checkable configuration), 128x256 tiles, grouped producer order."""
+    pl, X, W1, W2 = _run_case(1024, 8192, 8192, 8192, 3, 3, 0, 0, runs=2, fence=1, group_rows=8)
+    ys = oc.chain_reference(X, [W1, W2], keep=True)
+    for got, ref, name in ((pl.Y1, ys[0], "Y1"), (pl.Y2, ys[1], "Y2")):
+        mx, mean = oc.error_stats(got.cpu(), ref)
+        assert mx <= 2e-2 and mean <= 1e-3, (name, mx, mean)
+
+
+@pytest.mark.parametrize("rowpanel", [True, False])
+def test_chain_serialised_order_is_bit_exact(rowpanel):
+    """With a one-CTA producer the order in which consumer work becomes ready is deterministic: the queue must equal
+    the sequential protocol model's, entry for entry."""
+    from ctapp.pipeline import Chain
+    M, K, N1, N2 = 512, 256, 1024, 768
+    ch = Chain(M, K, [N1, N2], [0, 0], cfg=3, group_rows=2, scoreboard="rowpanel" if rowpanel else "tile", sms=1)
+    X, Ws = oc.make_chain_inputs(M, K, [N1, N2], seed=1)
+    ch.run(X.cuda(), [w.cuda() for w in Ws])
+    ch.check()
+    entries, tail, sb = oc.simulate_link(M, N1, N2, 128, 256, 128, 256, rowpanel, 2)
+    assert np.array_equal(ch.entries[1].cpu().numpy(), entries)
+    assert int(ch.tail[1].item()) == tail
+    assert np.array_equal(ch.sb[0].cpu().numpy(), sb)
+    mx, mean = oc.error_stats(ch.Y[1].cpu(), oc.chain_reference(X, Ws))
+    assert mx <= 2e-2 and mean <= 1e-3
+
+
+def test_chain_three_stages_one_gpu():
+    from ctapp.pipeline import Chain
+    M, K, widths = 384, 512, [768, 512, 1024]
+    ch = Chain(M, K, widths, [0, 0, 0], cfg=[3, 5, 3], group_rows=4)
+    X, Ws = oc.make_chain_inputs(M, K, widths, seed=2)
+    for _ in range(2):
+        ch.run(X.cuda(), [w.cuda() for w in Ws])
+        ch.check()
+    mx, mean = oc.error_stats(ch.Y[-1].cpu(), oc.chain_reference(X, Ws))
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+def test_missing_producer_times_out_cleanly():
+    """Fault injection on the host side: the consumer is launched although nothing will ever fill its queue.  Its bounded
+    wait must give up, report code 1 in the status buffer, and leave the context usable."""
+    from ctapp.ext import load, new_status
+    ext = load()
+    ext.set_wait_limit_ms(50)
+    try:
+        M, K, N = 256, 256, 512
+        X = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda"); W = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+        Y = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        ntiles = 2 * 2
+        entries = torch.full((ntiles,), -1, dtype=torch.int32, device="cuda")
+        head = torch.zeros(1, dtype=torch.int32, device="cuda"); tail = torch.zeros(1, dtype=torch.int32, device="cuda")
+        status = new_status("cuda")
+        ext.ctapp_gemm(X, W, Y, 3, entries, head, tail, None, None, None, None, None, None, 2, 0, 0, status=status)
+        torch.cuda.synchronize()
+        s = status.cpu().tolist()
+        assert s[0] == 1 and s[5] >= 1, s
+        # the context still works
+        Y2 = torch.empty_like(Y)
+        ext.gemm_tma(X, W, Y2, 3)
+        torch.cuda.synchronize()
+        assert torch.equal(Y2, torch.zeros_like(Y2))
+    finally:
+        ext.set_wait_limit_ms(2000)
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("case", [(1024, 8192, 8192, 8192, 3, 3, dict(fence=1, group_rows=8)), (4096, 8192, 8192, 8192, 3, 3, dict(fence=1, group_rows=8)),
+                                  (4096, 4096, 8192, 4096, 5, 3, dict(fence=1)), (2048, 8192, 8192, 10240, 3, 3, dict(scoreboard="tile", group_rows=8))])
+def test_chain_two_gpus(case):
+    M, K, N1, N2, c1, c2, kw = case
+    pl, X, W1, W2 = _run_case(M, K, N1, N2, c1, c2, 0, 1, runs=10, **kw)
+    if M <= 1024:
+        mx, mean = oc.error_stats(pl.Y2.cpu(), oc.chain_reference(X, [W1, W2]))
+        assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+@pytest.mark.multigpu(2)
+def test_negative_control_two_gpus():
+    """skip_wait makes the consumer ignore the queue; its output must then differ from the correct one somewhere, which shows
+    the comparison above can see a race."""
+    from ctapp.pipeline import Pipeline
+    M, K, N = 8192, 8192, 8192
+    pl = Pipeline(M, K, N, N, 3, 3, devA=0, devB=1, skip_wait=1, fence=1, group_rows=8)
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(M, K, generator=g).to(torch.bfloat16).to(pl.a)
+    W1 = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(pl.a)
+    W2 = (torch.randn(N, N, generator=g) / N ** 0.5).to(torch.bfloat16).to(pl.b)
+    with torch.cuda.device(pl.b):
+        pl.Y1.fill_(float("nan"))
+    torch.cuda.synchronize(pl.b)
+    pl.run(X, W1, W2)
+    pl.check()
+    assert torch.isnan(pl.Y2.float()).any(), "skipping the wait changed nothing: the test cannot see races"

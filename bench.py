@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Benchmark of the CTA-pipelined layer-per-GPU GEMM chain.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: an N-stage chain of bf16 linear layers, one stage per GPU, M = 8192 tokens, N = K = 8192, no activation,
+X ~ N(0,1), W_l ~ N(0, 1/K), seeded, fp32 accumulation, bf16 between stages.  Stage g's output tiles are stored straight
+into GPU g+1's memory by the GEMM epilogue and announced in that GPU's work queue; nothing else moves data.  At N = 1 the
+chain is one stage: one 8192^3 GEMM through the same work-queue protocol.  A step is one run of the whole chain.
+
+Prints ONE JSON line (rank 0): metric = chain TFLOP/s = N * 2*M*N*K / step time, whole job.  ``value`` is measured with the
+inputs resident in HBM; ``e2e`` is the same through the public API with X in pinned host memory (copied in every step) and
+the last stage's output copied back every step.  ``roofline`` is for the GEMM kernel (tensor-core bound), timed by CUDA
+events around each launch.  ``cpu_baseline`` / ``--impl reference`` time the reference's torch CPU path (fp32 ``F.linear``
+chain) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "cta-pipelining_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+NK = 8192
+CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+# DRAM traffic of one 8192^3 GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture summarised
+# in profiles/ (None until a capture of this kernel exists)
+GEMM_DRAM_TRAFFIC_BYTES = None
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops"), d.get("bf16_tflops_sustained"), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = float(r[2])
+                for name, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        busy = [c for c in sm if mx and c > 0.3 * mx] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_chain_reference(M, n_stages, reps, threads=None):
+    """The reference's CPU path for this workload: fp32 F.linear per stage, bf16 between stages.  Returns (best s, TFLOP/s)."""
+    from oracle import chain as oc
+    if threads:
+        torch.set_num_threads(threads)
+    X, Ws = oc.make_chain_inputs(M, NK, [NK] * n_stages, seed=0)
+    best = float("inf")
+    for _ in range(reps):
+        t = time.perf_counter()
+        oc.chain_reference(X, Ws)
+        best = min(best, time.perf_counter() - t)
+    return best, n_stages * 2 * M * NK * NK / best / 1e12
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's own CPU implementation of the path, on all host cores."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    M_s = min(args.m, 2048)                     # bounded sample: the first M_s token rows of the workload
+    n = max(args.gpus, 1)
+    ts = []
+    from oracle import chain as oc
+    torch.set_num_threads(cores)
+    X, Ws = oc.make_chain_inputs(M_s, NK, [NK] * n, seed=0)
+    for i in range(args.warmup + args.steps):
+        t = time.perf_counter()
+        oc.chain_reference(X, Ws)
+        dt = time.perf_counter() - t
+        if i >= args.warmup:
+            ts.append(dt)
+    ms = statistics.mean(ts) * 1e3
+    val = n * 2 * M_s * NK * NK / (ms * 1e-3) / 1e12
+    line = {"impl": "reference", "metric": "chain_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args, n),
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"first {M_s} of {args.m} token rows, all {n} stages, torch CPU fp32 F.linear chain"},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n):
+    return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
+                        + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
+            "M": args.m, "N": NK, "K": NK, "stages": n, "tile": "128x256x64", "parallelism": f"pp{n}",
+            "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    assert world == max(args.gpus, 1), f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run), got WORLD_SIZE={world}"
+    import torch.distributed as dist
+    from ctapp.pipeline import Chain, ChainStage
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+        gloo = dist.new_group(backend="gloo")
+    M, n = args.m, world
+    W_steps, K_steps = max(args.warmup, 3), args.steps
+    flops_step = n * 2 * M * NK * NK
+
+    def barrier():
+        if world > 1:
+            dist.barrier(group=gloo)
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=gloo)
+        return float(t.item())
+
+    # ---- inputs (seeded on the CPU; every rank draws the same stream and keeps its stage's weight)
+    g = torch.Generator().manual_seed(0)
+    X_host = torch.randn(M, NK, generator=g).to(torch.bfloat16).pin_memory() if rank == 0 else None
+    if rank != 0:
+        torch.randn(M, NK, generator=g)
+    Wmine = None
+    for s in range(n):
+        w = torch.randn(NK, NK, generator=g)
+        if s == rank:
+            Wmine = (w / NK ** 0.5).to(torch.bfloat16).to(dev)
+        del w
+    X_dev = X_host.to(dev) if rank == 0 else None
+    Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
+
+    if world == 1:
+        chain = Chain(M, NK, [NK], [local_rank], cfg=3, group_rows=16)
+        step = lambda: chain.run(X_dev, [Wmine])  # noqa: E731
+        checker = chain.check
+        launches_per_step = 2   # reset kernel + GEMM kernel
+    else:
+        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=3, group_rows=16)
+        step = lambda: stage.step(Wmine, X_dev)  # noqa: E731
+        checker = stage.check
+        launches_per_step = 2 * n
+
+    # ---- device-resident timing: W warm-up steps, then exactly K steps between barriers
+    for _ in range(W_steps):
+        step()
+    checker()
+    barrier()
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        torch.cuda.synchronize(dev)
+        a.record()
+        for _ in range(K_steps):
+            step()
+        b.record()
+        torch.cuda.synchronize(dev)
+        barrier()
+        ms_total = max_over_ranks(a.elapsed_time(b))
+        # keep the GPU busy a little longer so that the 100 ms sampler sees clocks under load
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize(dev)
+    checker()
+    ms_step = ms_total / K_steps
+    value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---- the GEMM kernel alone: CUDA events around each launch on the launching stream
+    # (with more than one stage a stage's kernel spans the whole pipelined run, so its duration is the step's)
+    kernel_ms = ms_step
+    if world == 1:
+        kt = []
+        for _ in range(K_steps):
+            chain.reset()
+            a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a2.record(); chain.enqueue(X_dev, [Wmine]); b2.record()
+            torch.cuda.synchronize(dev)
+            kt.append(a2.elapsed_time(b2))
+        checker()
+        kernel_ms = statistics.mean(kt)
+
+    # ---- end to end through the public API: X from pinned host memory in, last stage's Y out, every step
+    def e2e_step():
+        if rank == 0:
+            X_dev.copy_(X_host, non_blocking=True)
+        y = step()
+        if rank == n - 1:
+            Y_host.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize(dev)
+    barrier()
+    a3, b3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    a3.record()
+    for _ in range(K_steps):
+        e2e_step()
+    b3.record()
+    torch.cuda.synchronize(dev)
+    barrier()
+    e2e_ms = max_over_ranks(a3.elapsed_time(b3)) / K_steps
+    checker()
+
+    if rank != 0:
+        return
+    burst, sustained, kind = peaks()
+    line = {"metric": "chain_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": K_steps, "warmup": W_steps,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args, n), "clocks": clk.summary(),
+            "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": M * NK * 2, "d2h_bytes_per_step": M * NK * 2},
+            "gpu_launches": launches_per_step * K_steps}
+    if True:
+        ach = 2 * M * NK * NK / (kernel_ms * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst,
+                            "traffic": GEMM_DRAM_TRAFFIC_BYTES, "peak_kind": f"{kind} burst bf16 ({'kernel timed alone' if world == 1 else 'per GPU: one stage kernel spans the pipelined run'}, {kernel_ms:.3f} ms per launch)",
+                            "frac_of_sustained": ach / sustained, "kernel": "gemm_kernel<256>", "flop_per_launch": 2 * M * NK * NK}
+    if not args.no_cpu_baseline and world == 1:
+        reps = 3
+        best, tf = cpu_chain_reference(min(M, 8192), 1, reps, os.cpu_count())
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"one stage (M={min(M, 8192)}, N=K={NK}) of the chain, best of {reps}, torch CPU fp32 F.linear, {best:.2f} s"}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

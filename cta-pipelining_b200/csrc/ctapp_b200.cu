@@ -155,9 +155,9 @@ static int fill_common(GemmParams& p, const void* A, const void* B, int M, int N
 // ------------------------------------------------------------------------------------------ small kernels
 __global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb_len, int* ready, int ready_value) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
-  for (int k = i; k < q.cap; k += stride) q.entries[k] = -1;
+  if (q.entries) for (int k = i; k < q.cap; k += stride) q.entries[k] = -1;   // null: a pre-filled source queue keeps its ids and tail
   for (int k = i; k < sb_len; k += stride) sb[k] = pristine[k];
-  if (i == 0) { *q.head = 0; *q.tail = 0; }
+  if (i == 0) { *q.head = 0; if (q.entries) *q.tail = 0; }
   if (ready) {   // single CTA: everything above is ordered before the flag
     __threadfence_system();
     __syncthreads();
@@ -284,7 +284,7 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
 }
 
 int ctapp_chain_reset(ctapp_queue q, int* scoreboard, const int* pristine, int sb_len, int* ready_flag, int ready_value, int device, void* stream) {
-  ARG(q.entries && q.head && q.tail && q.cap > 0, "bad queue");
+  ARG(q.head && (!q.entries || (q.tail && q.cap > 0)), "bad queue");
   ARG(sb_len == 0 || (scoreboard && pristine), "scoreboard pointers are required when scoreboard_len > 0");
   GUARD(device);
   chain_reset_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(Queue{q.entries, q.head, q.tail, q.cap}, scoreboard, pristine, sb_len, ready_flag, ready_value);

@@ -251,8 +251,10 @@ class ChainModule:
         _check(self.lib.ctapp_chain_gemm(_ptr(X), _ptr(W), _ptr(Y), M, N, K, int(config_id), C.byref(a), dev, _stream(dev)))
 
     def chain_reset(self, entries, head, tail, scoreboard=None, pristine=None, ready_flag=None, ready_value=0):
-        q = Queue(_ptr(entries), _ptr(head), _ptr(tail), entries.numel())
-        dev = entries.device.index
+        """One kernel: entries = -1, head = tail = 0, scoreboard = pristine, then ready_flag = ready_value (release, system
+        scope).  entries None: only head is rewound (a pre-filled source queue)."""
+        q = Queue(_ptr(entries), _ptr(head), _ptr(tail), entries.numel() if entries is not None else 0)
+        dev = head.device.index
         _check(self.lib.ctapp_chain_reset(q, _ptr(scoreboard), _ptr(pristine), scoreboard.numel() if scoreboard is not None else 0,
                                           _ptr(ready_flag), int(ready_value), dev, _stream(dev)))
 

@@ -141,18 +141,17 @@ class Chain:
                 self.dep_off.append(None); self.dep_cons.append(None); self.sb.append(None); self.sb_pristine.append(None)
 
     def reset(self):
+        """One reset kernel per stage (queue entries = -1, head = tail = 0, scoreboard restored); stage g may write into
+        stage g+1's memory only after that stage's reset, which a stream event orders across GPUs."""
         L = len(self.widths)
         evs = [None] * L
         for g in range(L):
             with torch.cuda.device(self.devs[g]):
-                self.head[g].zero_()
-                if g > 0:
-                    self.entries[g].fill_(EMPTY); self.tail[g].zero_()
-                if self.sb[g] is not None:
-                    self.sb[g].copy_(self.sb_pristine[g])
-                evs[g] = torch.cuda.Event(); evs[g].record()
-        for g in range(L - 1):   # stage g may write into stage g+1's memory only after that stage's reset
-            if self.devs[g] != self.devs[g + 1]:
+                self.ext.chain_reset(None if g == 0 else self.entries[g], self.head[g], self.tail[g], self.sb[g], self.sb_pristine[g])
+                if g > 0 and self.devs[g - 1] != self.devs[g]:
+                    evs[g] = torch.cuda.Event(); evs[g].record()
+        for g in range(L - 1):
+            if evs[g + 1] is not None:
                 torch.cuda.current_stream(self.devs[g]).wait_event(evs[g + 1])
 
     def enqueue(self, X, Ws):
@@ -177,3 +176,82 @@ class Chain:
             torch.cuda.synchronize(d)
         for g, s in enumerate(self.status):
             check_status(s, f"chain stage {g}")
+
+
+class ChainStage:
+    """One stage of an N-stage chain, owned by one process (one process per GPU, ``torch.distributed`` initialised).
+
+    Rank g holds W_g and computes Y_g = Y_{g-1} W_g^T.  Its input buffer and its work queue live in its own memory and are
+    mapped into rank g-1, whose GEMM epilogue stores finished tiles straight into that buffer and publishes completed row
+    panels in that queue.  No collective is on the data path.  Re-running needs no host synchronisation between ranks:
+    every ``step`` first resets this rank's queue and then raises a ready flag in rank g-1's memory to the step number;
+    rank g-1's epilogue waits for that value before its first store of the step.
+    """
+
+    def __init__(self, M, K, widths, rank, world, device, group=None, cfg=3, group_rows=8, scoreboard="rowpanel"):
+        from ctapp.symm import symm_empty, view_ptr
+        assert len(widths) == world
+        self.ext = load()
+        self.M, self.rank, self.world, self.cfg = M, rank, world, cfg
+        self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
+        self.rowpanel = int(scoreboard == "rowpanel")
+        self.ext.preload(self.dev.index)
+        BM, BN = _tile(self.ext, cfg)
+        tm = -(-M // BM)
+        ins = [K] + list(widths[:-1])
+        self.k_in, self.n_out = ins[rank], widths[rank]
+        self.tn = -(-self.n_out // BN)
+        self.ntiles = tm * self.tn
+        i32 = dict(dtype=torch.int32)
+        first, last = rank == 0, rank == world - 1
+        # symmetric buffers (collective, same order on every rank)
+        self.Yin, h_y = symm_empty((M, self.k_in) if not first else (8,), torch.bfloat16, self.dev, group, rank)
+        self.entries_sym, h_e = symm_empty((self.ntiles,), torch.int32, self.dev, group, rank)
+        self.ctl, h_c = symm_empty((4,), torch.int32, self.dev, group, rank)       # [head, tail, ready, -]
+        self._hdls = (h_y, h_e, h_c)
+        self.head, self.tail, self.ready = self.ctl[0:1], self.ctl[1:2], self.ctl[2:3]
+        if first:
+            self.entries = producer_order(self.ntiles, self.tn, group_rows).to(self.dev)
+            self.tail.fill_(self.ntiles)
+        else:
+            self.entries = self.entries_sym
+            self.entries.fill_(EMPTY)
+        self.status = new_status(self.dev)
+        self.epoch = 0
+        if not last:
+            n_next = widths[rank + 1]
+            tn2 = -(-n_next // BN)
+            self.tn2 = tn2
+            off, cons, sb = build_deps(M, self.n_out, n_next, BM, BN, BM, BN, bool(self.rowpanel))
+            self.dep_off, self.dep_cons = off.to(self.dev), cons.to(self.dev)
+            self.sb_pristine = sb.to(self.dev); self.sb = self.sb_pristine.clone()
+            nxt = rank + 1
+            self.Yout = view_ptr(h_y.buffer_ptrs[nxt], (M, self.n_out), torch.bfloat16, self.dev)
+            self.dst_entries = view_ptr(h_e.buffer_ptrs[nxt], (tm * tn2,), torch.int32, self.dev)
+            ctl_next = view_ptr(h_c.buffer_ptrs[nxt], (4,), torch.int32, self.dev)
+            self.dst_head, self.dst_tail = ctl_next[0:1], ctl_next[1:2]
+        else:
+            self.tn2 = 0
+            self.dep_off = self.dep_cons = self.sb = self.sb_pristine = None
+            self.Yout = torch.empty(M, self.n_out, dtype=torch.bfloat16, device=self.dev)
+            self.dst_entries = self.dst_head = self.dst_tail = None
+        self.up_ready = None if first else view_ptr(h_c.buffer_ptrs[rank - 1], (4,), torch.int32, self.dev)[2:3]
+        torch.cuda.synchronize(self.dev)
+
+    def step(self, W, X=None):
+        """Enqueue one run of this stage.  Rank 0 passes the chain's input X; the other ranks read their input buffer."""
+        self.epoch += 1
+        e = self.epoch
+        first, last = self.rank == 0, self.rank == self.world - 1
+        with torch.cuda.device(self.dev):
+            self.ext.chain_reset(None if first else self.entries, self.head, self.tail, self.sb, self.sb_pristine,
+                                 ready_flag=self.up_ready, ready_value=e)
+            inp = X if first else self.Yin
+            self.ext.ctapp_gemm(inp, W, self.Yout, self.cfg, self.entries, self.head, self.tail, self.dep_off, self.dep_cons, self.sb,
+                                self.dst_entries, self.dst_head, self.dst_tail, self.tn, 0, 1, tiles_n2=self.tn2, rowpanel=self.rowpanel,
+                                status=self.status, dst_ready=None if last else self.ready, ready_value=e)
+        return self.Yout
+
+    def check(self):
+        torch.cuda.synchronize(self.dev)
+        check_status(self.status, f"chain stage {self.rank}")

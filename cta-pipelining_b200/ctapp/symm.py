@@ -47,6 +47,14 @@ def _shape(shape):
     return tuple(shape) if isinstance(shape, (tuple, list)) else (int(shape),)
 
 
+def view_ptr(ptr, shape, dtype, device):
+    """A torch tensor over foreign device memory (a peer's buffer mapped into this process): a typed pointer carrier for
+    the bindings, never read or written by torch itself."""
+    nbytes = _numel(shape) * torch.empty((), dtype=dtype).element_size()
+    dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
+    return torch.as_tensor(_RawCuda(ptr, nbytes), device=dev).view(dtype).view(_shape(shape))
+
+
 class _Allocation:
     """Device memory from the library's allocator (eligible for CUDA IPC), freed with the object."""
 

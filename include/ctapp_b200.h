@@ -89,8 +89,9 @@ typedef struct ctapp_chain_args {     /* ctapp.cuh:7-19 */
  * Y may be a peer address (the next GPU's input).  gemm_tma.cu:136-153 (ctapp_gemm). */
 int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int config_id,
                      const ctapp_chain_args* args, int device, void* stream);
-/* Reset a stage's queue for the next run (entries = -1, head = tail = 0, scoreboard = pristine) and then, if
- * ready_flag != NULL, release ready_flag[0] = ready_value at system scope (a flag in the upstream GPU's memory).
+/* Reset a stage's queue for the next run (entries = -1, head = tail = 0, scoreboard = pristine; q.entries == NULL
+ * keeps a pre-filled source queue's ids and tail and only rewinds head) and then, if ready_flag != NULL, release
+ * ready_flag[0] = ready_value at system scope (a flag in the upstream GPU's memory).
  * ctapp/pipeline.py:64-71 (Pipeline.reset), as one kernel. */
 int ctapp_chain_reset(ctapp_queue q, int* scoreboard, const int* scoreboard_pristine, int scoreboard_len,
                       int* ready_flag, int ready_value, int device, void* stream);

@@ -1,0 +1,182 @@
+"""The tensor-parallel boundary through the C ABI against the CPU oracle.
+
+One GPU plays every rank here (``LocalGroup`` with a repeated device, phases launched in dependency order so nothing waits
+on the device); with 2+ GPUs the same objects run one rank per GPU, concurrently.  Checked per case:
+  * x and out against the oracle's model of the device rounding sequence (>= 99 % of the elements within one bf16 ulp, and
+    max relative error <= 2e-2 / mean absolute error <= 1e-3 after normalising by the output RMS);
+  * x and out against the fp32 reference within the reference's own tolerance (max|a-b| / max|b| < 1e-2 for x, < 2e-2 for out);
+  * x bit-identical on all ranks; every tile flag of the owned panels and every panel flag == epoch; 128 arrivals per panel.
+"""
+import pytest
+import torch
+
+from oracle import boundary as ob
+from oracle import chain as oc
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
+
+
+def _ulp_frac(a, b):
+    return ((a.view(torch.int16).int() - b.view(torch.int16).int()).abs() <= 1).float().mean().item()
+
+
+def _setup(world, devices, max_M, K, n1, N2_, **kw):
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundary
+    grp = LocalGroup(devices)
+    Kr, N2r = K // world, N2_ // world
+    return [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", devices[r]), protocol="v5", max_M=max_M, n1=n1,
+                          fusion="serial", **kw) for r in range(world)]
+
+
+def _forward_and_check(bds, M, K, n1, N2_, seed, use_resid=True):
+    from ctapp.tp4 import forward_lockstep
+    world = len(bds)
+    Kr, N2r = K // world, N2_ // world
+    Wd, gamma, Wq = ob.make_weights(seed=seed, K=K, N2_=N2_, n1=n1)
+    h, resid = ob.make_inputs(M, seed=seed + 100, K=K, n1=n1)
+    if not use_resid:
+        resid = None
+    sh = [ob.shard_weights(Wd, Wq, gamma, r, world) for r in range(world)]
+    devs = [bd.dev for bd in bds]
+    outs = forward_lockstep(bds, [h[:, r * Kr:(r + 1) * Kr].contiguous().to(devs[r]) for r in range(world)],
+                            [resid.to(devs[r]) if resid is not None else None for r in range(world)],
+                            [sh[r][0].to(devs[r]) for r in range(world)], [sh[r][2].to(devs[r]) for r in range(world)])
+    for bd in bds:
+        bd.check()
+    x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, world)
+    x_ref, out_ref = ob.boundary_reference(h, Wd, resid, gamma, Wq)
+    xs = [bd.x().cpu() for bd in bds]
+    for r in range(world):
+        assert torch.equal(xs[r], xs[0]), f"x differs between rank {r} and rank 0"
+    assert _ulp_frac(xs[0], x_model) >= 0.99, _ulp_frac(xs[0], x_model)
+    mx, mean = oc.error_stats(xs[0], x_model)
+    assert mx <= 2e-2 and mean <= 1e-3, ("x vs model", mx, mean)
+    assert rel(xs[0], x_ref) < 1e-2, rel(xs[0], x_ref)
+    out = torch.cat([o.cpu() for o in outs], dim=1)
+    assert not torch.isnan(out.float()).any()
+    mx, mean = oc.error_stats(out, out_model)
+    assert mx <= 2e-2 and mean <= 1e-3, ("out vs model", mx, mean)
+    assert _ulp_frac(out, out_model) >= 0.98, _ulp_frac(out, out_model)
+    assert rel(out, out_ref) < 2e-2, rel(out, out_ref)
+    # protocol state
+    P = M // 128
+    for r, bd in enumerate(bds):
+        Pr = ob.panels_owned(M, r, world)
+        assert (bd.tile_flags[:, :Pr, :].cpu() == bd.epoch).all(), f"rank {r}: a tile flag of an owned panel != epoch {bd.epoch}"
+        assert (bd.panel_flag[:P].cpu() == bd.epoch).all(), f"rank {r}: a panel flag != epoch {bd.epoch}"
+        own = [m for m in range(P) if m % world == r]
+        assert (bd.panel_done[own].cpu() == (n1 // 256) * 4).all()
+        assert int(bd.epoch_dev.item()) == bd.epoch
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_boundary_one_gpu_plays_all_ranks(world):
+    K, n1, N2_ = 1024 * world if world < 8 else 2048, 512, 256 * world
+    bds = _setup(world, [0] * world, 1024, K, n1, N2_)
+    for seed, M in enumerate((1024, 256, 640, 128), start=3):   # variable M on one instance, fresh weights per call
+        _forward_and_check(bds, M, K, n1, N2_, seed)
+
+
+def test_boundary_no_residual_and_tile128():
+    bds = _setup(2, [0, 0], 512, 512, 768, 512, resid=False, qkv_tile=128, down_tail=0)
+    _forward_and_check(bds, 512, 512, 768, 512, 11, use_resid=False)
+    _forward_and_check(bds, 384, 512, 768, 512, 12, use_resid=False)
+
+
+def test_boundary_hidden_8192_one_rank_vs_oracle():
+    """The real hidden size (8192) with a reduced K so the CPU oracle finishes in seconds."""
+    bds = _setup(1, [0], 512, 1024, 8192, 1280)
+    _forward_and_check(bds, 512, 1024, 8192, 1280, 21)
+
+
+def test_boundary_single_rank_public_forward_and_floor():
+    """world 1 through the public ``forward`` (serial fusion), eager and CUDA graph, plus the protocol-free floor."""
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundary
+    M, K, n1, N2_ = 256, 512, 512, 512
+    Wd, gamma, Wq = ob.make_weights(seed=5, K=K, N2_=N2_, n1=n1)
+    h, resid = ob.make_inputs(M, seed=6, K=K, n1=n1)
+    wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, 0, 1)
+    x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, 1)
+    for use_graph in (False, True):
+        bd = CtappBoundary(M, K, N2_, 0, 1, LocalGroup([0]), torch.device("cuda", 0), protocol="v5", n1=n1, fusion="serial", use_graph=use_graph)
+        bd.set_weights(wd.cuda(), wqf.cuda())
+        for i in range(5):
+            out = bd.forward(h.cuda(), resid.cuda())
+            bd.check()
+            assert _ulp_frac(out.cpu(), out_model) >= 0.98 and _ulp_frac(bd.x().cpu(), x_model) >= 0.99, (use_graph, i)
+    fl = CtappBoundary(M, K, N2_, 0, 1, LocalGroup([0]), torch.device("cuda", 0), protocol=False, n1=n1)
+    y = fl.forward(h.cuda(), None, wd.cuda(), wqf.cuda())
+    torch.cuda.synchronize()
+    ref = ((h.float() @ wd.float().t()).to(torch.bfloat16).float() @ wqf.float().t()).to(torch.bfloat16)
+    assert _ulp_frac(y.cpu(), ref) >= 0.98
+
+
+def test_reducer_missing_producer_times_out_cleanly():
+    """Fault injection on the host: the owner reducer is launched although no producer will raise its tile flags.  Its
+    bounded wait must give up with code 3 and leave the context usable."""
+    from ctapp.ext import load_tp4
+    ext = load_tp4()
+    ext.set_wait_limit_ms(50)
+    try:
+        bds = _setup(1, [0], 256, 256, 512, 256)
+        bd = bds[0]
+        bd.epoch += 1
+        ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, 256, bd.role_ctr)
+        bd._reduce_v5(256, None, 1)
+        torch.cuda.synchronize()
+        s = bd.status.cpu().tolist()
+        assert s[0] == 3 and s[3] == 1, s
+        with pytest.raises(RuntimeError):
+            bd.check()
+        _forward_and_check(_setup(1, [0], 256, 256, 512, 256), 256, 256, 512, 256, 31)
+    finally:
+        ext.set_wait_limit_ms(2000)
+
+
+def test_add_rmsnorm_baseline_kernel():
+    from ctapp.ext import load_tp4
+    from ctapp.tp4 import rmsnorm_gamma
+    ext = load_tp4()
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(64, 8192, generator=g).to(torch.bfloat16).cuda(); r = torch.randn(64, 8192, generator=g).to(torch.bfloat16).cuda()
+    gamma = (0.5 + torch.rand(8192, generator=g)).to(torch.bfloat16).cuda()
+    x, y = torch.empty_like(a), torch.empty_like(a)
+    ext.add_rmsnorm(a, r, gamma, x, y)
+    torch.cuda.synchronize()
+    xr = a + r
+    assert torch.equal(x, xr)
+    assert _ulp_frac(y, rmsnorm_gamma(xr, gamma)) >= 0.99
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl")])
+def test_boundary_two_gpus_concurrent(world, fusion):
+    """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundary
+    K, n1, N2_, max_M = 4096, 8192, 2560, 2048
+    grp = LocalGroup(list(range(world)))
+    Kr, N2r = K // world, N2_ // world
+    bds = [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", r), protocol="v5", max_M=max_M, n1=n1, fusion=fusion) for r in range(world)]
+    Wd, gamma, Wq = ob.make_weights(seed=1, K=K, N2_=N2_, n1=n1)
+    sh = [ob.shard_weights(Wd, Wq, gamma, r, world) for r in range(world)]
+    wds = [sh[r][0].to(bds[r].dev) for r in range(world)]; wqs = [sh[r][2].to(bds[r].dev) for r in range(world)]
+    for it, M in enumerate((2048, 512, 1024, 2048, 2048)):
+        h, resid = ob.make_inputs(M, seed=40 + it, K=K, n1=n1)
+        outs = [bds[r].forward(h[:, r * Kr:(r + 1) * Kr].contiguous().to(bds[r].dev), resid.to(bds[r].dev), wds[r], wqs[r]) for r in range(world)]
+        for bd in bds:
+            bd.check()
+        x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, world)
+        xs = [bd.x().cpu() for bd in bds]
+        assert all(torch.equal(x, xs[0]) for x in xs)
+        assert _ulp_frac(xs[0], x_model) >= 0.99
+        out = torch.cat([o.cpu() for o in outs], dim=1)
+        assert _ulp_frac(out, out_model) >= 0.98
+        mx, mean = oc.error_stats(out, out_model)
+        assert mx <= 2e-2 and mean <= 1e-3

@@ -222,9 +222,8 @@ def main():
         torch.cuda.synchronize(dev)
         barrier()
         ms_total = max_over_ranks(a.elapsed_time(b))
-        # keep the GPU busy a little longer so that the 100 ms sampler sees clocks under load
-        t_end = time.time() + 0.6
-        while time.time() < t_end:
+        # keep the GPU busy a little longer so that the 100 ms sampler sees clocks under load (same step count on every rank)
+        for _ in range(int(min(2000, 600.0 / max(ms_total / K_steps, 0.05)))):
             step()
         torch.cuda.synchronize(dev)
     checker()

@@ -178,6 +178,24 @@ class Chain:
             check_status(s, f"chain stage {g}")
 
 
+def stage_plan(M, K, widths, rank, tile=(128, 256)):
+    """Sizes of stage ``rank`` of an N-stage chain and of the link to its successor: a pure function every rank evaluates
+    for itself and for its neighbours (the queue a stage publishes into must have exactly the successor's tile count)."""
+    BM, BN = tile
+    world = len(widths)
+    ins = [K] + list(widths[:-1])
+    tm = -(-M // BM)
+    tn = -(-widths[rank] // BN)
+    plan = {"rank": rank, "k_in": ins[rank], "n_out": widths[rank], "tiles_m": tm, "tiles_n": tn, "ntiles": tm * tn,
+            "first": rank == 0, "last": rank == world - 1}
+    if rank + 1 < world:
+        tn2 = -(-widths[rank + 1] // BN)
+        plan.update(tiles_n2=tn2, dst_cap=tm * tn2, dst_rows=M, dst_cols=widths[rank])
+    else:
+        plan.update(tiles_n2=0, dst_cap=0, dst_rows=0, dst_cols=0)
+    return plan
+
+
 class ChainStage:
     """One stage of an N-stage chain, owned by one process (one process per GPU, ``torch.distributed`` initialised).
 
@@ -197,13 +215,10 @@ class ChainStage:
         self.rowpanel = int(scoreboard == "rowpanel")
         self.ext.preload(self.dev.index)
         BM, BN = _tile(self.ext, cfg)
-        tm = -(-M // BM)
-        ins = [K] + list(widths[:-1])
-        self.k_in, self.n_out = ins[rank], widths[rank]
-        self.tn = -(-self.n_out // BN)
-        self.ntiles = tm * self.tn
-        i32 = dict(dtype=torch.int32)
-        first, last = rank == 0, rank == world - 1
+        plan = stage_plan(M, K, widths, rank, (BM, BN))
+        tm = plan["tiles_m"]
+        self.k_in, self.n_out, self.tn, self.ntiles = plan["k_in"], plan["n_out"], plan["tiles_n"], plan["ntiles"]
+        first, last = plan["first"], plan["last"]
         # symmetric buffers (collective, same order on every rank)
         self.Yin, h_y = symm_empty((M, self.k_in) if not first else (8,), torch.bfloat16, self.dev, group, rank)
         self.entries_sym, h_e = symm_empty((self.ntiles,), torch.int32, self.dev, group, rank)

@@ -20,6 +20,7 @@ import logging
 import os
 import statistics
 import sys
+import time
 import traceback
 
 import torch
@@ -557,7 +558,7 @@ def _entry(rank, world, port, fn, args, queue, backend):
     os._exit(code)  # skip process-group teardown (it can block when a peer has already gone)
 
 
-def launch(fn, world, port, *args, backend="nccl"):
+def launch(fn, world, port, *args, backend="nccl", grace_s=10.0):
     """Run fn(rank, world, dev, group_name, *args) in ``world`` processes (one per GPU; backend "gloo" runs them on the
     CPU); returns (per-rank results, bad).  A rank that dies or raises makes ``bad`` true and its result None; the
     others are not left waiting (reference ctapp/tp4.py:767-790)."""
@@ -569,17 +570,26 @@ def launch(fn, world, port, *args, backend="nccl"):
     for p in procs:
         p.start()
     results, got = [None] * world, 0
+    failed_at = None
     while got < world:
         try:
-            r, st, res = q.get(timeout=5)
+            r, st, res = q.get(timeout=1)
             results[r] = res if st == "ok" else None
             got += 1
+            if st != "ok" and failed_at is None:
+                failed_at = time.time()
         except _q.Empty:
             if all(not p.is_alive() for p in procs):
                 break
+            if failed_at is None and any(p.exitcode not in (None, 0) for p in procs):
+                failed_at = time.time()
+        # a rank has failed: the others may be blocked in a collective with it; give them a grace period, then stop them
+        if failed_at is not None and time.time() - failed_at > grace_s:
+            break
     for p in procs:
-        p.join(timeout=30)
+        p.join(timeout=0.5 if failed_at is not None else 30)
         if p.is_alive():
             p.kill()
+            p.join(timeout=5)
     bad = got < world or any(r is None for r in results)
     return results, bad

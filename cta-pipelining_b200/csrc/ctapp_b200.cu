@@ -195,6 +195,32 @@ __global__ void pingpong_kernel(int* mine, int* other, unsigned long long* out, 
   }
 }
 
+// ------------------------------------------------------------------------------------------ allocation-free reducer scratch
+// Working memory of ctapp_tp_reduce_noalloc: the owner reducer's per-row accumulators (fp32) followed by its per-panel
+// arrival counters (int32).  It lives in the library image, so every GPU that loads the library carries these
+// 66 048 bytes until the process exits, and every call on a GPU shares them.
+constexpr int kNoAllocMaxM = 16384;
+constexpr size_t kNoAllocRowssBytes = static_cast<size_t>(kNoAllocMaxM) * sizeof(float);
+constexpr size_t kNoAllocBytes = kNoAllocRowssBytes + (kNoAllocMaxM / 128) * sizeof(int);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// Device address of the scratch array on `device` (which must be current).  In host code the array's name is only a
+// handle for the runtime, never an address a kernel could use; the address is asked for once per device and remembered.
+static int noalloc_scratch_ptr(int device, unsigned char** out) {
+  static std::mutex mu;
+  static unsigned char* cache[64] = {};
+  if (device < 0 || device >= 64) return fail(-1, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return fail(static_cast<int>(e), "cudaGetSymbolAddress(reducer scratch) on device %d: %s", device, cudaGetErrorString(e));
+    cache[device] = static_cast<unsigned char*>(p);
+  }
+  *out = cache[device];
+  return 0;
+}
+
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
@@ -383,6 +409,54 @@ int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
   p.limit_ns = limit_ns();
   if (a->M == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (a->world) {
+    case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
+    case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);
+    case 4: return launch_reduce<4>(p, a->blocks, a->threads, s);
+    default: return launch_reduce<8>(p, a->blocks, a->threads, s);
+  }
+}
+
+// The owner reducer for hosts that must not allocate device memory: same arguments and results as ctapp_tp_reduce, but
+// the per-step working memory (row accumulators, panel arrival counters) is the library's own fixed array instead of
+// caller buffers, and this call clears it itself.  args->rowss_local / args->panel_done / args->unit_ctr are ignored.
+// Nothing here allocates: one cudaGetSymbolAddress per device (first call only), two cudaMemsetAsync, one launch.
+int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* stream) {
+  ARG(a, "null args");
+  ARG(a->world == 1 || a->world == 2 || a->world == 4 || a->world == 8, "world %d is not supported (1 | 2 | 4 | 8)", a->world);
+  ARG(a->rank >= 0 && a->rank < a->world, "bad rank %d", a->rank);
+  ARG(a->M >= 0 && a->M % 128 == 0 && a->n1 > 0 && a->n1 % 256 == 0, "bad shape M=%d n1=%d", a->M, a->n1);
+  ARG(a->M <= kNoAllocMaxM, "M=%d is beyond the built-in scratch of ctapp_tp_reduce_noalloc (at most %d rows); use ctapp_tp_reduce with caller buffers",
+      a->M, kNoAllocMaxM);
+  ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
+  ARG(a->tile_flags, "null tile_flags");
+  ARG(a->tail_cols >= 0 && a->tail_cols <= a->n1 / 256, "bad tail_cols %d", a->tail_cols);
+  GUARD(device);
+  unsigned char* scratch = nullptr;
+  if (int r = noalloc_scratch_ptr(device, &scratch)) return r;
+  ReduceParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.n1 = a->n1; p.rank = a->rank; p.world = a->world;
+  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
+  p.tile_flags = a->tile_flags;
+  for (int d = 0; d < a->world; d++) {
+    ARG(a->inbox[d] && a->peer_x[d] && a->peer_rowss[d] && a->peer_panel_flag[d], "missing peer buffer %d", d);
+    p.inbox[d] = static_cast<const uint4*>(a->inbox[d]);
+    p.x[d] = static_cast<uint4*>(a->peer_x[d]);
+    p.rowss[d] = a->peer_rowss[d];
+    p.panel_flag[d] = a->peer_panel_flag[d];
+  }
+  p.resid = static_cast<const uint4*>(a->resid);
+  p.rowss_local = reinterpret_cast<float*>(scratch);
+  p.panel_done = reinterpret_cast<int*>(scratch + kNoAllocRowssBytes);
+  p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
+  p.unit_ctr = nullptr; p.trace = a->trace; p.status = a->status;
+  p.limit_ns = limit_ns();
+  if (a->M == 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: the accumulators and counters of this step's rows start from zero
+  CU_OK(cudaMemsetAsync(p.rowss_local, 0, static_cast<size_t>(a->M) * sizeof(float), s));
+  CU_OK(cudaMemsetAsync(p.panel_done, 0, static_cast<size_t>(a->M / 128) * sizeof(int), s));
   switch (a->world) {
     case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
     case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);

@@ -131,6 +131,7 @@ _SIGS = {
     "ctapp_tp_down": (C.c_int, [C.POINTER(TpDownArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_qkv": (C.c_int, [C.POINTER(TpQkvArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_reduce": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
+    "ctapp_tp_reduce_noalloc": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "ctapp_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "ctapp_kernel_info": (C.c_int, [C.c_int, C.c_char_p, C.c_int]),
@@ -382,6 +383,22 @@ class Tp4Module:
         a.unit_ctr, a.trace, a.status = _ptr(unit_ctr), _ptr(red_trace), _ptr(status)
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
+
+    def tp4_reduce_noalloc(self, M, rank, world, epoch, blocks, tile_flags, resid=None, peer_x=(), epoch_dev=None, inbox_ptrs=(),
+                           peer_rowss=(), peer_panel_flag=(), panels_per_owner=0, threads=1024, tail_cols=0, n1=8192, status=None):
+        """The owner reducer without caller scratch buffers and without any allocation (``ctapp_tp_reduce_noalloc``): for hosts
+        that may not allocate device memory while running.  M <= 16384; calls that overlap on the GPU race on the shared
+        built-in scratch; make the first call on a device outside stream capture."""
+        a = TpReduceArgs()
+        a.M, a.n1, a.rank, a.world, a.epoch, a.epoch_dev = int(M), int(n1), int(rank), int(world), int(epoch), _ptr(epoch_dev)
+        a.blocks, a.threads = int(blocks), int(threads)
+        a.tile_flags = _ptr(tile_flags)
+        a.inbox, a.peer_x = _ptr_array(inbox_ptrs), _ptr_array(peer_x)
+        a.peer_rowss, a.peer_panel_flag = _ptr_array(peer_rowss), _ptr_array(peer_panel_flag)
+        a.resid = _ptr(resid)
+        a.panels_per_owner, a.tail_cols, a.status = int(panels_per_owner), int(tail_cols), _ptr(status)
+        dev = tile_flags.device.index
+        _check(self.lib.ctapp_tp_reduce_noalloc(C.byref(a), dev, _stream(dev)))
 
     def tp4_step(self, epoch_dev, rowss_local, panel_done, M, role_ctr=None):
         dev = epoch_dev.device.index

@@ -145,6 +145,23 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 
+/* Owner reducer for callers that cannot allocate device memory.  No counterpart in the reference.
+ * Some hosts of this library never get to call cudaMalloc once they are running: an inference server that hands the
+ * whole GPU to its own block pool at start-up, or a plugin called on a path where an allocation (which may synchronise
+ * the device or fail in a full GPU) is not acceptable.  For them this variant of ctapp_tp_reduce keeps the reducer's
+ * working memory -- the per-row fp32 accumulators and the per-panel arrival counters that ctapp_tp_reduce takes as
+ * rowss_local / panel_done -- in a fixed array inside the library (66 048 bytes, resident on every GPU that loads the
+ * library until the process exits).  The caller passes inputs and outputs exactly as for ctapp_tp_reduce;
+ * args->rowss_local, args->panel_done and args->unit_ctr are ignored, and no ctapp_tp_step is needed for them: the
+ * call zeroes the part of the array it uses (stream-ordered, before the kernel).
+ *   Limit: M <= 16384 rows; larger M is refused with an error naming the limit.
+ *   The first call on a device looks up the array's device address (one cudaGetSymbolAddress, no allocation); make
+ *   that first call outside any stream capture.
+ *   All calls on a GPU share the one array: two calls whose kernels overlap on the GPU (different streams) race on
+ *   it.  Issue them on one stream, or order them with events.
+ * The call performs no cudaMalloc / cudaFree and uses no allocating library routine. */
+int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* args, int device, void* stream);
+
 /* epoch_dev[0] += 1; zero rowss_local[0:M], panel_done[0:M/128] and role_ctr[0:2].  gemm_tp4.cu:362-372 (tp4_step). */
 int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream);
 

@@ -33,6 +33,7 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 NK = 8192
+GEMM_CFG = 10   # CTA-pair tcgen05 kernel, 256 x 256 x 64 tiles
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
                "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 # DRAM traffic of one 8192^3 GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture summarised
@@ -136,7 +137,7 @@ def run_reference(args, rank):
 def workload_config(args, n):
     return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
                         + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
-            "M": args.m, "N": NK, "K": NK, "stages": n, "tile": "128x256x64", "parallelism": f"pp{n}",
+            "M": args.m, "N": NK, "K": NK, "stages": n, "tile": "256x256x64 per CTA pair (cta_group::2)", "parallelism": f"pp{n}",
             "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)"}
 
 
@@ -195,12 +196,12 @@ def main():
     Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
 
     if world == 1:
-        chain = Chain(M, NK, [NK], [local_rank], cfg=3, group_rows=16)
+        chain = Chain(M, NK, [NK], [local_rank], cfg=GEMM_CFG, group_rows=8)
         step = lambda: chain.run(X_dev, [Wmine])  # noqa: E731
         checker = chain.check
         launches_per_step = 2   # reset kernel + GEMM kernel
     else:
-        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=3, group_rows=16)
+        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=GEMM_CFG, group_rows=8)
         step = lambda: stage.step(Wmine, X_dev)  # noqa: E731
         checker = stage.check
         launches_per_step = 2 * n
@@ -280,7 +281,7 @@ def main():
         ach = 2 * M * NK * NK / (kernel_ms * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst,
                             "traffic": GEMM_DRAM_TRAFFIC_BYTES, "peak_kind": f"{kind} burst bf16 ({'kernel timed alone' if world == 1 else 'per GPU: one stage kernel spans the pipelined run'}, {kernel_ms:.3f} ms per launch)",
-                            "frac_of_sustained": ach / sustained, "kernel": "gemm_kernel<256>", "flop_per_launch": 2 * M * NK * NK}
+                            "frac_of_sustained": ach / sustained, "kernel": "gemm2_kernel", "flop_per_launch": 2 * M * NK * NK}
     if not args.no_cpu_baseline and world == 1:
         reps = 3
         best, tf = cpu_chain_reference(min(M, 8192), 1, reps, os.cpu_count())

@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "gemm_sm100.cuh"
+#include "gemm2_sm100.cuh"
 #include "reduce_sm100.cuh"
 
 using namespace ctapp;
@@ -94,13 +95,15 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long lon
 // ------------------------------------------------------------------------------------------ configurations
 // Reference ids 0-9 name wgmma tiles (64|128 x 128|256).  A 64-row UMMA tile has no place here (one CTA drives a
 // 128-lane TMEM accumulator), so every id resolves to the 128-row tile with the same width.
+// Ids 10 and up are this library's own: 10 = CTA pair (cta_group::2) working on a 256 x 256 tile.
 static int cfg_bn(int id) {
   switch (id) {
     case 0: case 1: case 5: case 7: return 128;
-    case 2: case 3: case 4: case 6: case 8: case 9: return 256;
+    case 2: case 3: case 4: case 6: case 8: case 9: case 10: return 256;
     default: return 0;
   }
 }
+static bool cfg_pair(int id) { return id == 10; }
 static int sm_count(int dev) {
   static int cache[64];
   if (dev < 0 || dev >= 64) return 0;
@@ -138,17 +141,49 @@ static int launch_gemm(GemmParams& p, int bn, int sms, int pdl, int dev, cudaStr
   return 0;
 }
 
-static int fill_common(GemmParams& p, const void* A, const void* B, int M, int N, int K, int bn) {
+// pair: the schedule's tile is 256 rows (two CTAs), and each CTA loads half of the B tile's rows
+static int fill_common(GemmParams& p, const void* A, const void* B, int M, int N, int K, int bn, bool pair = false) {
   memset(&p, 0, sizeof(p));
   ARG(A && B, "null operand");
   ARG(M > 0 && N > 0 && K > 0, "bad shape M=%d N=%d K=%d", M, N, K);
   ARG(K % 8 == 0 && N % 8 == 0, "K=%d and N=%d must be multiples of 8", K, N);
+  ARG(!pair || bn == 256, "the CTA-pair kernel has 256-column tiles");
   p.M = M; p.N = N; p.K = K;
-  p.tiles_m = (M + BM - 1) / BM;
+  p.panels = (M + BM - 1) / BM;
+  p.tiles_m = pair ? (M + 2 * BM - 1) / (2 * BM) : p.panels;
   p.tiles_n = (N + bn - 1) / bn;
   p.num_tiles = p.tiles_m * p.tiles_n;
   if (int r = make_tmap(&p.tmA, A, M, K, K, BK, BM)) return r;
-  if (int r = make_tmap(&p.tmB, B, N, K, K, BK, bn)) return r;
+  if (int r = make_tmap(&p.tmB, B, N, K, K, BK, pair ? bn / 2 : bn)) return r;
+  return 0;
+}
+
+static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t stream) {
+  const int nsm = sm_count(dev);
+  int pairs = (sms > 0 && sms < nsm ? sms : nsm) / 2;
+  if (pairs > p.num_tiles) pairs = p.num_tiles;
+  if (pairs < 1) return 0;
+  p.limit_ns = limit_ns();
+  CU_OK(cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Gemm2Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+  na++;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel, p));
   return 0;
 }
 
@@ -235,6 +270,11 @@ int ctapp_get_wait_limit_ms(void) { return static_cast<int>(limit_ns() / 1000000
 int ctapp_config_info(int config_id, char* buf, int buf_len) {
   const int bn = cfg_bn(config_id);
   ARG(bn && buf && buf_len > 0, "bad config_id %d", config_id);
+  if (cfg_pair(config_id)) {
+    snprintf(buf, buf_len, "tcgen05 cta_group::2 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=%d cluster=2", 2 * BM, bn, BK,
+             kThreads, Gemm2Cfg::kSmemBytes, Gemm2Cfg::kStages, 2 * bn);
+    return 0;
+  }
   const int stages = bn == 256 ? GemmCfg<256>::kStages : GemmCfg<128>::kStages;
   const unsigned smem = bn == 256 ? GemmCfg<256>::kSmemBytes : GemmCfg<128>::kSmemBytes;
   snprintf(buf, buf_len, "tcgen05 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=%d", BM, bn, BK, kThreads, smem, stages, 2 * bn);
@@ -245,7 +285,7 @@ int ctapp_occupancy(int config_id) { return cfg_bn(config_id) ? 1 : fail(-1, "ba
 int ctapp_kernel_info(int which, char* buf, int buf_len) {
   ARG(buf && buf_len > 0, "null buffer");
   cudaFuncAttributes a;
-  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : (const void*)tp_reduce_kernel<4, 2>;
+  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel : (const void*)tp_reduce_kernel<4, 2>;
   CU_OK(cudaFuncGetAttributes(&a, fn));
   snprintf(buf, buf_len, "regs=%d local=%zu static_smem=%zu max_threads=%d", a.numRegs, a.localSizeBytes, a.sharedSizeBytes, a.maxThreadsPerBlock);
   return 0;
@@ -262,8 +302,10 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 1>));
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
+  CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel));
   if (int r = prepare_kernel<256>()) return r;
   if (int r = prepare_kernel<128>()) return r;
+  CU_OK(cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
   return 0;
 }
 
@@ -273,12 +315,14 @@ int ctapp_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int c
   ARG(bn, "bad config_id %d", config_id);
   ARG(Y, "null output");
   GUARD(device);
+  const bool pair = cfg_pair(config_id);
   GemmParams p;
-  if (int r = fill_common(p, X, W, M, N, K, bn)) return r;
+  if (int r = fill_common(p, X, W, M, N, K, bn, pair)) return r;
   if (int r = make_tmap(&p.tmD[0], Y, M, N, N, kStoreCols, kStageRows)) return r;
   p.mode = kModePlain;
   p.order = kOrderGrouped;
-  p.group_rows = group_rows > 0 ? group_rows : 8;
+  p.group_rows = group_rows > 0 ? group_rows : (pair ? 8 : 16);
+  if (pair) return launch_gemm2(p, sms, 0, device, static_cast<cudaStream_t>(stream));
   return launch_gemm(p, bn, sms, 0, device, static_cast<cudaStream_t>(stream));
 }
 
@@ -287,8 +331,9 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   ARG(bn, "bad config_id %d", config_id);
   ARG(a && Y, "null argument");
   GUARD(device);
+  const bool pair = cfg_pair(config_id);
   GemmParams p;
-  if (int r = fill_common(p, X, W, M, N, K, bn)) return r;
+  if (int r = fill_common(p, X, W, M, N, K, bn, pair)) return r;
   ARG(a->src.entries && a->src.head && a->src.tail, "source queue pointers are required");
   ARG(a->src.cap == p.num_tiles, "source queue capacity %d != number of tiles %d", a->src.cap, p.num_tiles);
   ARG(a->tiles_n == p.tiles_n, "tiles_n %d does not match N=%d with tile width %d", a->tiles_n, N, bn);
@@ -306,6 +351,7 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   p.tiles_n2 = a->tiles_n2; p.rowpanel = a->rowpanel; p.skip_wait = a->skip_wait;
   p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
   p.status = a->status; p.stamps = a->stamps;
+  if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream));
   return launch_gemm(p, bn, a->sms, 0, device, static_cast<cudaStream_t>(stream));
 }
 
@@ -324,8 +370,9 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
   ARG(a->mode == 0 || a->mode == 7, "tp_down mode %d is not supported (0 | 7)", a->mode);
   ARG(a->world >= 1 && a->world <= CTAPP_MAX_WORLD && a->rank >= 0 && a->rank < a->world, "bad rank %d / world %d", a->rank, a->world);
   GUARD(device);
+  const bool pair = a->cta_pair != 0;
   GemmParams p;
-  if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, 256)) return r;
+  if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, 256, pair)) return r;
   ARG(a->N % 256 == 0, "N=%d must be a multiple of 256", a->N);
   p.status = a->status; p.stamps = a->trace;
   p.pdl_trigger = a->pdl_trigger; p.pdl_wait = a->pdl;
@@ -351,6 +398,7 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
       p.peer_tile_flags[d] = a->peer_tile_flags[d];
     }
   }
+  if (pair) return launch_gemm2(p, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
   return launch_gemm(p, 256, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
 }
 
@@ -359,9 +407,10 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
   ARG(a->mode == 0 || a->mode == 5, "tp_qkv mode %d is not supported (0 | 5)", a->mode);
   ARG(a->tile == 256 || a->tile == 128 || a->tile == 0, "bad tile %d", a->tile);
   const int bn = a->tile == 128 ? 128 : 256;
+  const bool pair = a->cta_pair != 0 && bn == 256;
   GUARD(device);
   GemmParams p;
-  if (int r = fill_common(p, a->X, a->W, a->M, a->N, a->K, bn)) return r;
+  if (int r = fill_common(p, a->X, a->W, a->M, a->N, a->K, bn, pair)) return r;
   ARG(a->Y, "null output");
   if (int r = make_tmap(&p.tmD[0], a->Y, a->M, a->N, a->N, kStoreCols, kStageRows)) return r;
   p.status = a->status; p.stamps = a->trace;
@@ -378,6 +427,7 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
     p.panel_flag = nullptr;
     p.pdl_wait = a->pdl;
   }
+  if (pair) return launch_gemm2(p, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
   return launch_gemm(p, bn, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
 }
 

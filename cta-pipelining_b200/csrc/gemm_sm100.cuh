@@ -40,7 +40,8 @@ struct alignas(64) GemmParams {
   CUtensorMap tmB;                 // B (N, K) row-major bf16, box 64 x BN
   CUtensorMap tmD[kMaxWorld];      // D (rows, N) row-major bf16, box 64 x 32; one per destination
   int M, N, K;
-  int tiles_m, tiles_n, num_tiles;
+  int tiles_m, tiles_n, num_tiles;   // tile rows / columns of the schedule (CTA-pair kernel: 256-row tiles)
+  int panels;                        // 128-row panels of M
   int mode, order, group_rows, tail_cols;
   // chain
   Queue src;

@@ -21,7 +21,7 @@ CSRC = os.path.join(ROOT, "csrc")
 LIB_PATH = os.path.join(ROOT, "libctapp_b200.so")
 BD = BD4 = ROOT   # build directory (the reference kept one per module; here one library serves both)
 SOURCES = ["ctapp_b200.cu"]
-HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
+HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 STATUS_INTS = 8
@@ -84,14 +84,15 @@ class TpDownArgs(C.Structure):
                 ("raster", C.c_int), ("swizzle", C.c_int), ("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int),
                 ("epoch", C.c_int), ("epoch_dev", C.c_void_p), ("dst_ptrs", C.c_void_p * MAX_WORLD), ("dst_rows", C.c_int),
                 ("peer_tile_flags", C.c_void_p * MAX_WORLD), ("panels_per_owner", C.c_int), ("sms", C.c_int),
-                ("pdl_trigger", C.c_int), ("pdl", C.c_int), ("tail_cols", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p)]
+                ("pdl_trigger", C.c_int), ("pdl", C.c_int), ("tail_cols", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p),
+                ("cta_pair", C.c_int)]
 
 
 class TpQkvArgs(C.Structure):
     _fields_ = [("X", C.c_void_p), ("W", C.c_void_p), ("Y", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
                 ("raster", C.c_int), ("swizzle", C.c_int), ("mode", C.c_int), ("epoch", C.c_int), ("epoch_dev", C.c_void_p),
                 ("panel_flag", C.c_void_p), ("rowss", C.c_void_p), ("eps", C.c_float), ("sms", C.c_int), ("pdl", C.c_int),
-                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p)]
+                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p), ("cta_pair", C.c_int)]
 
 
 class TpReduceArgs(C.Structure):
@@ -327,7 +328,7 @@ class Tp4Module:
 
     def tp4_down(self, A, W, D, raster, swizzle, mode, rank, world, epoch, tile_cnt_mc=0, tile_cnt=None, partials_mc=0, x_mc=0,
                  resid=None, rowss_mc=0, panel_cnt_mc=0, sms=0, epoch_dev=None, rowss_mc_base=0, rowss_stride=0, d_ptr=0,
-                 dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None):
+                 dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None, cta_pair=0):
         A, W = _bf16_matrix(A, "A"), _bf16_matrix(W, "W")
         if mode not in (0, 7):
             raise RuntimeError(f"tp4_down: mode {mode} is not available in this build (0 | 7)")
@@ -342,12 +343,12 @@ class Tp4Module:
         a.dst_ptrs, a.dst_rows = _ptr_array(dst_ptrs), int(dst_rows)
         a.peer_tile_flags, a.panels_per_owner = _ptr_array(peer_tile_flags), int(panels_per_owner)
         a.sms, a.pdl_trigger, a.pdl, a.tail_cols = int(sms), int(pdl_trigger), int(pdl), int(tail_cols)
-        a.trace, a.status = _ptr(trace), _ptr(status)
+        a.trace, a.status, a.cta_pair = _ptr(trace), _ptr(status), int(cta_pair)
         dev = A.device.index
         _check(self.lib.ctapp_tp_down(C.byref(a), dev, _stream(dev)))
 
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
-                tile=256, trace=0, status=None, eps=1e-5, **unsupported):
+                tile=256, trace=0, status=None, eps=1e-5, cta_pair=0, **unsupported):
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
         if mode not in (0, 5):
             raise RuntimeError(f"tp4_qkv: mode {mode} is not available in this build (0 | 5)")
@@ -361,7 +362,7 @@ class Tp4Module:
         a.panel_flag = _ptr(panel_cnt) if mode == 5 else None
         a.rowss = _ptr(rowss)
         a.eps, a.sms, a.pdl, a.tile = float(eps), int(sms), int(pdl), int(tile)
-        a.trace, a.status = _ptr(trace), _ptr(status)
+        a.trace, a.status, a.cta_pair = _ptr(trace), _ptr(status), int(cta_pair)
         dev = X.device.index
         _check(self.lib.ctapp_tp_qkv(C.byref(a), dev, _stream(dev)))
 

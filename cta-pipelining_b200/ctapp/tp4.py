@@ -82,6 +82,8 @@ class CtappBoundary:
                      single GPU plays every rank).
     use_graph: forwards are captured into CUDA graphs keyed by (parity, M); inputs are copied into static buffers
     before each replay (``graph_bind`` captures the caller's tensors instead).
+    cta_pair: both GEMMs run as CTA pairs (``cta_group::2``, 256-row tiles; the protocol's unit stays the 128-row panel);
+    False = one CTA per 128-row tile.
     ``group_name``: a torch.distributed group name (one process per GPU) or a ``ctapp.symm.LocalGroup`` (one process
     drives every rank's GPU).
     """
@@ -89,7 +91,7 @@ class CtappBoundary:
     def __init__(self, M, Kr, N2r, rank, world, group_name, device, resid=True, protocol="v5", use_graph=False, R=None,
                  qkv_raster=2, qkv_swizzle=1, max_M=None, down_raster=None, red_threads=1024, red_blocks=None, red_variant=1,
                  fusion="none", qkv_tile=256, role_rows=4, down_swizzle=1, pdl_trigger=None, trace=None, role_stages=0, steal=False,
-                 down_tail="auto", graph_bind=False, n1=N1, eps=EPS):
+                 down_tail="auto", graph_bind=False, n1=N1, eps=EPS, cta_pair=True):
         assert M % 128 == 0 and n1 % 256 == 0, (M, n1)
         assert protocol in (True, False, "v3", "v5"), protocol
         assert world in (1, 2, 4, 8), f"world {world} is not supported"
@@ -101,7 +103,7 @@ class CtappBoundary:
         assert down_tail == "auto" or (isinstance(down_tail, int) and 0 <= down_tail <= n1 // 256), down_tail
         self.ext = load_tp4()
         self.M, self.Kr, self.N2r, self.rank, self.world = M, Kr, N2r, rank, world
-        self.n1, self.eps = n1, eps
+        self.n1, self.eps, self.cta_pair = n1, eps, int(bool(cta_pair))
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
         self.use_resid, self.protocol, self.use_graph, self.v5 = resid, bool(protocol), use_graph, bool(protocol)
         self.group = group_name
@@ -187,12 +189,12 @@ class CtappBoundary:
         self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms,
                           epoch_dev=self.epoch_dev, dst_ptrs=self._dst_ptrs, dst_rows=self.ppo * 128, peer_tile_flags=self._peer_tf,
                           panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, trace=self._tr(self.trace_down),
-                          tail_cols=self._tail(M), status=self.status)
+                          tail_cols=self._tail(M), status=self.status, cta_pair=self.cta_pair)
 
     def _qkv_v5(self, Wq, M, parity):
         self.ext.tp4_qkv(self.xbufs[parity][:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 5, 0, self.panel_flag, 1,
                          self.rowss[parity], sms=self.qkv_sms, pdl=1 if self.fusion == "pdl" else 0, epoch_dev=self.epoch_dev,
-                         tile=self.qkv_tile, trace=self._tr(self.trace_qkv), status=self.status, eps=self.eps)
+                         tile=self.qkv_tile, trace=self._tr(self.trace_qkv), status=self.status, eps=self.eps, cta_pair=self.cta_pair)
 
     def _enqueue_v5(self, h_r, resid, parity, Wd, Wq, M):
         cur = torch.cuda.current_stream(self.dev)
@@ -216,8 +218,9 @@ class CtappBoundary:
         if self._floor_y is None:
             self._floor_y = torch.empty(self.max_M, self.n1, dtype=DTYPE, device=self.dev)
         self.ext.tp4_down(h_r, Wd, self._floor_y[:M], self.down_raster, self.down_swizzle, 0, self.rank, self.world, 0, sms=self.sms,
-                          tail_cols=self._tail(M))
-        self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile)
+                          tail_cols=self._tail(M), cta_pair=self.cta_pair)
+        self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile,
+                         cta_pair=self.cta_pair)
 
     # ---- public API
     def warmup(self):

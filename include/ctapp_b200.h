@@ -49,7 +49,9 @@ int ctapp_ipc_get_handle(void* ptr, unsigned char handle64[64], int device);
 int ctapp_ipc_open(const unsigned char handle64[64], void** out, int device);
 int ctapp_ipc_close(void* ptr, int device);
 
-/* ---- GEMM configurations (csrc/gemm_tma.cu:116-126, 155-165) ---- */
+/* ---- GEMM configurations (csrc/gemm_tma.cu:116-126, 155-165) ----
+ * ids 0-9 are the reference's; each resolves to a one-CTA tcgen05 tile 128 x {128|256} x 64.  id 10 (no counterpart in
+ * the reference) is the CTA-pair kernel: a cluster of two CTAs, cta_group::2, protocol tile 256 x 256 x 64. */
 int ctapp_config_info(int config_id, char* buf, int buf_len);   /* text contains "tile BMxBNxBK" */
 int ctapp_occupancy(int config_id);                              /* resident CTAs per SM */
 
@@ -109,6 +111,7 @@ typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0
   int sms, pdl_trigger, pdl, tail_cols;
   unsigned long long* trace;
   int* status;
+  int cta_pair;                            /* 1 = two CTAs per 256-row tile (cta_group::2), 0 = one CTA per 128-row tile */
 } ctapp_tp_down_args;
 int ctapp_tp_down(const ctapp_tp_down_args* args, int device, void* stream);
 
@@ -123,6 +126,7 @@ typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 
   int sms, pdl, tile;                      /* tile: 256 | 128 */
   unsigned long long* trace;
   int* status;
+  int cta_pair;                            /* as in ctapp_tp_down_args; needs tile 256 */
 } ctapp_tp_qkv_args;
 int ctapp_tp_qkv(const ctapp_tp_qkv_args* args, int device, void* stream);
 

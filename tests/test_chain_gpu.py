@@ -41,6 +41,8 @@ def _run_case(M, K, N1, N2, cfg1, cfg2, devA, devB, runs=3, **kw):
 
 
 @pytest.mark.parametrize("case", [(256, 512, 512, 768, 3, 3, {}), (512, 1024, 1024, 1024, 5, 3, dict(group_rows=2)),
+                                  (512, 512, 1024, 768, 10, 10, {}), (768, 512, 768, 1024, 10, 3, dict(group_rows=2)), (640, 256, 512, 512, 3, 10, dict(scoreboard="tile")),
+                                  (384, 512, 512, 512, 10, 10, dict(group_rows=1)),
                                   (384, 512, 768, 512, 3, 5, dict(scoreboard="tile")), (1000, 520, 1000, 264, 5, 5, dict(group_rows=8))])
 def test_chain_one_gpu_small(case):
     M, K, N1, N2, c1, c2, kw = case
@@ -50,26 +52,29 @@ def test_chain_one_gpu_small(case):
     assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
 
 
-def test_chain_one_gpu_headline_config_vs_oracle():
-    """M=1024, N=K=8192 (the CPU-checkable configuration), 128x256 tiles, grouped producer order."""
-    pl, X, W1, W2 = _run_case(1024, 8192, 8192, 8192, 3, 3, 0, 0, runs=2, fence=1, group_rows=8)
+@pytest.mark.parametrize("cfg", [3, 10])
+def test_chain_one_gpu_headline_config_vs_oracle(cfg):
+    """M=1024, N=K=8192 (the CPU-checkable configuration), 128x256 tiles and CTA-pair 256x256 tiles, grouped producer order."""
+    pl, X, W1, W2 = _run_case(1024, 8192, 8192, 8192, cfg, cfg, 0, 0, runs=2, fence=1, group_rows=8 if cfg == 3 else 4)
     ys = oc.chain_reference(X, [W1, W2], keep=True)
     for got, ref, name in ((pl.Y1, ys[0], "Y1"), (pl.Y2, ys[1], "Y2")):
         mx, mean = oc.error_stats(got.cpu(), ref)
         assert mx <= 2e-2 and mean <= 1e-3, (name, mx, mean)
 
 
+@pytest.mark.parametrize("cfg", [3, 10])
 @pytest.mark.parametrize("rowpanel", [True, False])
-def test_chain_serialised_order_is_bit_exact(rowpanel):
+def test_chain_serialised_order_is_bit_exact(rowpanel, cfg):
     """With a one-CTA producer the order in which consumer work becomes ready is deterministic: the queue must equal
     the sequential protocol model's, entry for entry."""
     from ctapp.pipeline import Chain
     M, K, N1, N2 = 512, 256, 1024, 768
-    ch = Chain(M, K, [N1, N2], [0, 0], cfg=3, group_rows=2, scoreboard="rowpanel" if rowpanel else "tile", sms=1)
+    BMt = 256 if cfg == 10 else 128
+    ch = Chain(M, K, [N1, N2], [0, 0], cfg=cfg, group_rows=2, scoreboard="rowpanel" if rowpanel else "tile", sms=2 if cfg == 10 else 1)
     X, Ws = oc.make_chain_inputs(M, K, [N1, N2], seed=1)
     ch.run(X.cuda(), [w.cuda() for w in Ws])
     ch.check()
-    entries, tail, sb = oc.simulate_link(M, N1, N2, 128, 256, 128, 256, rowpanel, 2)
+    entries, tail, sb = oc.simulate_link(M, N1, N2, BMt, 256, BMt, 256, rowpanel, 2)
     assert np.array_equal(ch.entries[1].cpu().numpy(), entries)
     assert int(ch.tail[1].item()) == tail
     assert np.array_equal(ch.sb[0].cpu().numpy(), sb)
@@ -118,6 +123,8 @@ def test_missing_producer_times_out_cleanly():
 
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("case", [(1024, 8192, 8192, 8192, 3, 3, dict(fence=1, group_rows=8)), (4096, 8192, 8192, 8192, 3, 3, dict(fence=1, group_rows=8)),
+                                  (1024, 8192, 8192, 8192, 10, 10, dict(fence=1, group_rows=4)), (4096, 8192, 8192, 8192, 10, 10, dict(fence=1, group_rows=8)),
+                                  (4096, 8192, 8192, 8192, 10, 3, dict(fence=1, group_rows=8)),
                                   (4096, 4096, 8192, 4096, 5, 3, dict(fence=1)), (2048, 8192, 8192, 10240, 3, 3, dict(scoreboard="tile", group_rows=8))])
 def test_chain_two_gpus(case):
     M, K, N1, N2, c1, c2, kw = case

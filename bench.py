@@ -37,8 +37,8 @@ GEMM_CFG = 10   # CTA-pair tcgen05 kernel, 256 x 256 x 64 tiles
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
                "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 # DRAM traffic of one 8192^3 GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture summarised
-# in profiles/gemm_kernel_256_chain_stage.md; the capture is of an M=2048 launch and traffic grows in proportion to M
-GEMM_DRAM_TRAFFIC_BYTES = int(4 * 283.67e6)   # 283.67 MB measured at M=2048 (profiles/), scaled by 8192 / 2048 rows
+# in profiles/gemm2_kernel_chain_stage.md; the capture is of an M=2048 launch and traffic grows in proportion to M
+GEMM_DRAM_TRAFFIC_BYTES = int(4 * 272.67e6)   # 272.67 MB measured at M=2048 (profiles/gemm2_kernel_chain_stage.md), scaled by 8192 / 2048 rows
 
 
 def peaks():

@@ -206,6 +206,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
+    ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
+                    "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
     ap.add_argument("--R", type=int, default=4, help="boundary: SMs reserved for the owner reducer")
     args = ap.parse_args()
@@ -257,13 +259,16 @@ def main():
     X_dev = X_host.to(dev) if rank == 0 else None
     Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
 
+    gr = args.group_rows
+    gr = (8 if world == 1 else 2) if gr == "auto" else (gr if gr == "ramp" else int(gr))
+    args.group_rows = gr
     if world == 1:
-        chain = Chain(M, NK, [NK], [local_rank], cfg=GEMM_CFG, group_rows=8)
+        chain = Chain(M, NK, [NK], [local_rank], cfg=GEMM_CFG, group_rows=args.group_rows)
         step = lambda: chain.run(X_dev, [Wmine])  # noqa: E731
         checker = chain.check
         launches_per_step = 2   # reset kernel + GEMM kernel
     else:
-        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=GEMM_CFG, group_rows=8)
+        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=GEMM_CFG, group_rows=args.group_rows)
         step = lambda: stage.step(Wmine, X_dev)  # noqa: E731
         checker = stage.check
         launches_per_step = 2 * n

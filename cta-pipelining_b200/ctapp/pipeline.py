@@ -46,14 +46,49 @@ def build_deps(M, N1, N2, BM1, BN1, BM2, BN2, rowpanel=True):
     return offsets.int(), consumers.int(), init.int()
 
 
+def ramp_groups(tm, peak=8):
+    """Group sizes 1, 1, 2, 4, ..., peak, ..., 4, 2, 1, 1 summing to ``tm`` tile rows: small groups first so that the first
+    row panels complete (and the next stage starts) early, large groups in the middle for L2 reuse of the weight panels,
+    small groups last so that little work is left for the next stage once this one has finished."""
+    up, g = [1, 1], 2
+    while g < peak:
+        up.append(g); g *= 2
+    sizes = []
+    head, tail = [], []
+    left = tm
+    for a in up:                       # take the ramp from both ends while rows remain
+        for side in (head, tail):
+            if left >= a and left - a >= 0 and (left - a >= peak or left <= 2 * sum(up)):
+                side.append(a); left -= a
+            if left == 0:
+                break
+        if left == 0:
+            break
+    while left > 0:
+        a = min(peak, left)
+        sizes.append(a); left -= a
+    return head + sizes + tail[::-1]
+
+
 def producer_order(P, tn1, group_rows):
-    """Tile ids in the order the first stage works through them: groups of ``group_rows`` tile rows, n-major inside a
-    group (reference ctapp/pipeline.py:48-51).  group_rows == 0 is ascending ids."""
+    """Tile ids in the order the first stage works through them: groups of tile rows, n-major inside a group (reference
+    ctapp/pipeline.py:48-51 for a constant group size).  ``group_rows``: 0 = ascending ids; an int = constant group size;
+    "ramp" or a list of group sizes = variable groups (``ramp_groups``)."""
     if not group_rows:
         return torch.arange(P, dtype=torch.int32)
-    t = torch.arange(P)
-    m, n = t // tn1, t % tn1
-    return torch.argsort(((m // group_rows) * tn1 + n) * group_rows + m % group_rows, stable=True).int()
+    tm = P // tn1
+    if isinstance(group_rows, int):
+        t = torch.arange(P)
+        m, n = t // tn1, t % tn1
+        return torch.argsort(((m // group_rows) * tn1 + n) * group_rows + m % group_rows, stable=True).int()
+    sizes = ramp_groups(tm) if group_rows == "ramp" else list(group_rows)
+    assert sum(sizes) == tm and all(s > 0 for s in sizes), (sizes, tm)
+    out, m0 = [], 0
+    for g in sizes:
+        rows = torch.arange(m0, m0 + g)
+        out.append((rows[None, :] * tn1 + torch.arange(tn1)[:, None]).reshape(-1))   # n-major: for each n, the g rows
+        m0 += g
+    return torch.cat(out).int()
 
 
 def _tile(ext, cfg):

@@ -151,3 +151,42 @@ def test_negative_control_two_gpus():
     pl.run(X, W1, W2)
     pl.check()
     assert torch.isnan(pl.Y2.float()).any(), "skipping the wait changed nothing: the test cannot see races"
+
+
+@pytest.mark.multigpu(2)
+def test_gated_harness_and_methods_two_gpus():
+    """The comparison methods give the chain's result (micro-batching bit for bit: same library GEMM on row slices; tensor
+    parallelism within bf16 tolerance), and the gate really holds the GPUs: a slow host between gate and launch does not
+    change the measured time."""
+    import time
+    from ctapp import methods as mt
+    from ctapp.timing import measure
+    M, N = 1024, 2048
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(M, N, generator=g).to(torch.bfloat16).to(mt.dev(0))
+    W1 = (torch.randn(N, N, generator=g) / N ** 0.5).to(torch.bfloat16)
+    W2 = (torch.randn(N, N, generator=g) / N ** 0.5).to(torch.bfloat16)
+    one = mt.OneGpuCublas(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(0)))
+    one.enqueue(); torch.cuda.synchronize(0)
+    ref = one.result().cpu()
+    mb = mt.MicroBatchCublas(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(1)), 256)
+    mb.enqueue(); torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+    mx, mean = oc.error_stats(mb.result().cpu(), ref)
+    assert mx <= 2e-2 and mean <= 1e-3
+    tp = mt.TensorParallel2(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(1)))
+    tp.enqueue(); torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+    mx, mean = oc.error_stats(tp.result().cpu(), ref)
+    assert mx <= 2e-2 and mean <= 2e-3, (mx, mean)
+    ct = mt.Ctapp(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(1)), 10, 10, 2)
+    t_fast = measure(ct, reps=5, warmup=2)[0]
+    ct.pl.check()
+    mx, mean = oc.error_stats(ct.result().cpu(), ref)
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+    class SlowHost(mt.Ctapp):
+        def enqueue(self):
+            time.sleep(0.01)
+            super().enqueue()
+    slow = SlowHost(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(1)), 10, 10, 2)
+    t_slow = measure(slow, reps=5, warmup=2)[0]
+    assert t_slow < 3 * t_fast + 200, (t_fast, t_slow)     # microseconds: the 10 ms host sleep is outside the window

@@ -107,7 +107,7 @@ class CtappBoundary:
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
         self.use_resid, self.protocol, self.use_graph, self.v5 = resid, bool(protocol), use_graph, bool(protocol)
         self.group = group_name
-        self.R = R or 4
+        self.R = R or (8 if world >= 4 else 4)   # measured on B200 at M=4096: TP2 best with 4, TP4 and TP8 with 8
         self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
         self.nsm = torch.cuda.get_device_properties(self.dev).multi_processor_count
         self.sms = self.nsm - self.R

@@ -159,10 +159,12 @@ def run_boundary(args, rank, world, local_rank):
     tp4.GLOO = dist.new_group(backend="gloo")
     M = args.m if args.m != 8192 else 4096
     t = world
-    Kr, N2r = tp4.K_FFN // t, tp4.N2 // t
+    Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
+    kfull = Kr * t
+    akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4)
     g = torch.Generator().manual_seed(0)
     # per-rank shards drawn directly (the full 28672-wide weights never exist in one place; parity is covered by the tests)
-    Wd_r = (torch.randn(tp4.N1, Kr, generator=g) * tp4.K_FFN ** -0.5).to(torch.bfloat16).to(dev)
+    Wd_r = (torch.randn(tp4.N1, Kr, generator=g) * kfull ** -0.5).to(torch.bfloat16).to(dev)
     gamma = (0.5 + torch.rand(tp4.N1, generator=g)).to(torch.bfloat16).to(dev)
     Wq_r = (torch.randn(N2r, tp4.N1, generator=g) * tp4.N1 ** -0.5).to(torch.bfloat16).to(dev)
     Wqf_r = tp4.fold_gamma(Wq_r, gamma)
@@ -170,11 +172,11 @@ def run_boundary(args, rank, world, local_rank):
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
     iters, warm = max(args.steps, 10), max(args.warmup, 3)
     res = {}
-    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol="v5", max_M=M, fusion=args.fusion, R=args.R or None)
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol="v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
-    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=args.R or None)
+    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=args.R or None, **akw)
     res["two_gemm_floor"] = tp4.time_step(lambda: fl.forward(h_r, None, Wd_r, Wqf_r), dev, iters, warm)
     st = tp4.NcclFusedNormBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
     res["cublas_nccl_fusednorm"] = tp4.time_step(lambda: st.forward(h_r, resid), dev, iters, warm)
@@ -189,7 +191,7 @@ def run_boundary(args, rank, world, local_rank):
         flops = 2 * M * Kr * tp4.N1 + 2 * M * tp4.N1 * N2r
         burst, sustained, kind = peaks()
         b2b = res["ctapp"][1]
-        print(json.dumps({"workload": f"TP{t} layer boundary, M={M}, down K={Kr} N=8192 -> reduce + residual + RMSNorm -> QKV N={N2r}",
+        print(json.dumps({"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
                           "n_gpus": t, "fusion": args.fusion, "R": bd.R, "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
                           "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
                           "tflops_per_gpu_b2b": flops / (b2b * 1e-3) / 1e12, "frac_of_burst_peak": flops / (b2b * 1e-3) / 1e12 / burst,
@@ -209,6 +211,7 @@ def main():
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
+    ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
     ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

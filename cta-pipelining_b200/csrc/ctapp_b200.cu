@@ -415,7 +415,10 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
   if (int r = make_tmap(&p.tmD[0], a->Y, a->M, a->N, a->N, kStoreCols, kStageRows)) return r;
   p.status = a->status; p.stamps = a->trace;
   p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
-  p.order = a->raster == 2 ? kOrderNFast : kOrderMFastTail;
+  // raster 2: n fastest (panel by panel); 3: groups of `swizzle` tile rows, n-major inside a group (wide outputs: keeps a
+  // weight panel in L2 across the group's rows); otherwise m fastest
+  p.order = a->raster == 2 ? kOrderNFast : a->raster == 3 ? kOrderGrouped : kOrderMFastTail;
+  p.group_rows = a->swizzle > 0 ? a->swizzle : 1;
   p.tail_cols = 0;
   p.rowss = a->rowss; p.inv_k = 1.0f / static_cast<float>(a->K); p.eps = a->eps;
   if (a->mode == 5) {

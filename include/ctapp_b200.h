@@ -118,7 +118,7 @@ int ctapp_tp_down(const ctapp_tp_down_args* args, int device, void* stream);
 typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 and 5 */
   const void* X; const void* W; void* Y;   /* X (M,K) local, written by the owner reducers; W (N,K) gamma-folded; Y (M,N) */
   int M, N, K;
-  int raster, swizzle, mode;
+  int raster, swizzle, mode;               /* raster 2: n fastest; 3: groups of `swizzle` tile rows, n-major inside; else m fastest */
   int epoch; const int* epoch_dev;
   const int* panel_flag;                   /* [M/128], value flags */
   const float* rowss;                      /* [M] row sums of squares of X; NULL = no scaling */

@@ -201,7 +201,8 @@ __global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb
 }
 
 template <int W> static int launch_reduce(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
-  tp_reduce_kernel<W, (W > 4 ? 1 : 2)><<<blocks, threads, 0, s>>>(p);
+  if (p.x_mc) tp_reduce_kernel<W, (W > 4 ? 1 : 2), true><<<blocks, threads, 0, s>>>(p);
+  else tp_reduce_kernel<W, (W > 4 ? 1 : 2)><<<blocks, threads, 0, s>>>(p);
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -459,6 +460,11 @@ int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
   p.rowss_local = a->rowss_local; p.panel_done = a->panel_done;
   p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
   p.unit_ctr = a->unit_ctr; p.trace = a->trace; p.status = a->status;
+  if (a->x_mc || a->rowss_mc || a->panel_flag_mc) {   // NVLS variant: all three multicast addresses or none
+    ARG(a->x_mc && a->rowss_mc && a->panel_flag_mc, "the NVLS variant needs x_mc, rowss_mc and panel_flag_mc");
+    ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
+    p.x_mc = static_cast<uint4*>(a->x_mc); p.rowss_mc = a->rowss_mc; p.panel_flag_mc = a->panel_flag_mc;
+  }
   p.limit_ns = limit_ns();
   if (a->M == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -534,6 +540,46 @@ int ctapp_add_rmsnorm(const void* a, const void* resid, const void* gamma, void*
   GUARD(device);
   add_rmsnorm_kernel<<<M, 256, n1 * 2, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(resid), static_cast<const uint4*>(gamma),
                                                                            static_cast<uint4*>(x_out), static_cast<uint4*>(y_out), n1, eps);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ NVLS probes
+int ctapp_mm_red_u32(void* mc, int n, unsigned v, int device, void* stream) {
+  ARG(mc && n > 0, "bad arguments");
+  GUARD(device);
+  mm_red_u32_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned*>(mc), n, v);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_mm_red_f32(void* mc, const float* src, int n, int device, void* stream) {
+  ARG(mc && src && n > 0, "bad arguments");
+  GUARD(device);
+  mm_red_f32_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<float*>(mc), src, n);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_mm_st_bf16(void* mc, const void* src, int n, int device, void* stream) {
+  ARG(mc && src && n > 0 && n % 8 == 0, "bad arguments (n must be a multiple of 8 bf16)");
+  GUARD(device);
+  mm_st_bf16_kernel<<<(n / 8 + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(mc), static_cast<const uint4*>(src), n / 8);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_mm_ld_reduce_bf16(const void* mc, void* out, int n, int device, void* stream) {
+  ARG(mc && out && n > 0 && n % 8 == 0, "bad arguments (n must be a multiple of 8 bf16)");
+  GUARD(device);
+  mm_ld_reduce_bf16_kernel<<<(n / 8 + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(mc), static_cast<uint4*>(out), n / 8);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_mm_order_stress(void* data_mc, const void* data_local, int* flag_mc, const int* flag_local, unsigned* ack_mc, const unsigned* ack_local,
+                          int rank, int world, int iters, int slots, int* result, int device, void* stream) {
+  ARG(data_mc && data_local && flag_mc && flag_local && ack_mc && ack_local && result, "null buffer");
+  ARG(world >= 2 && rank >= 0 && rank < world && iters > 0 && slots > 0 && slots <= 128, "bad arguments");
+  GUARD(device);
+  mm_order_stress_kernel<<<slots, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(data_mc), static_cast<const uint4*>(data_local), flag_mc,
+                                                                            flag_local, ack_mc, ack_local, rank, world, iters, result, limit_ns());
   CU_OK(cudaGetLastError());
   return 0;
 }

@@ -112,6 +112,34 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) { int o; asm 
 __device__ __forceinline__ int atom_add_relaxed_sys(int* p, int v) { int o; asm volatile("atom.relaxed.sys.global.add.s32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v) : "memory"); return o; }
 __device__ __forceinline__ int atom_add_relaxed_gpu(int* p, int v) { int o; asm volatile("atom.relaxed.gpu.global.add.s32 %0, [%1], %2;" : "=r"(o) : "l"(p), "r"(v) : "memory"); return o; }
 
+// ---- NVLS: stores / reductions on a multicast address are replicated (or combined) inside the NVSwitch
+__device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {   // 16 raw bytes to every GPU of the multicast group
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+__device__ __forceinline__ void multimem_st_f32x4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st_release_b32(int* mc, int v) {
+  asm volatile("multimem.st.release.sys.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_add_u32(unsigned* mc, unsigned v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_release_add_u32(unsigned* mc, unsigned v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_add_f32(float* mc, float v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+// 8 bf16 from every GPU of the group, summed in fp32 inside the switch, returned as 4 packed bf16x2
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+
 // ------------------------------------------------------------------------------------------ bounded waits
 // Records the first give-up of a launch in the status buffer (first writer wins; later ones only count).
 __device__ __forceinline__ void report_status(int* status, int code, int what, int expected, int seen) {

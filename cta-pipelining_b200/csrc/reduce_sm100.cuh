@@ -29,6 +29,10 @@ struct ReduceParams {
   unsigned long long* trace;
   int* status;
   long long limit_ns;
+  // NVLS variant: multicast addresses of the x buffer, the row-sum buffer and the panel flags (null = unicast pushes)
+  uint4* x_mc;
+  float* rowss_mc;
+  int* panel_flag_mc;
 };
 
 // unit u -> (owned panel j, n-tile, quarter), following the producer order "m-fast head, panel-major tail"
@@ -48,7 +52,9 @@ __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
   return s;
 }
 
-template <int W, int ROWS>
+// MC: the pushes to every rank (x rows, row sums, panel flags) are single multimem stores on a multicast address, replicated
+// by the NVSwitch, instead of one unicast store per rank; everything else is the same kernel.
+template <int W, int ROWS, bool MC = false>
 __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p) {
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
   const int P = p.M / 128;
@@ -109,10 +115,14 @@ __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p
         }
         const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
         const size_t xoff = xoff0 + static_cast<size_t>(r + rr) * row_vecs;
+        if (MC) {
+          multimem_st_v4(p.x_mc + xoff, ov);
+        } else {
 #pragma unroll
-        for (int d = 1; d <= W; d++) {   // remote copies first, the local one last
-          const int dst = (p.rank + d) % W;
-          st_relaxed_sys_v4(p.x[dst] + xoff, ov);
+          for (int d = 1; d <= W; d++) {   // remote copies first, the local one last
+            const int dst = (p.rank + d) % W;
+            st_relaxed_sys_v4(p.x[dst] + xoff, ov);
+          }
         }
         float ss = sumsq_bf16x8(ov);
 #pragma unroll
@@ -130,16 +140,71 @@ __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p
       if (lane == 0) fence_acq_rel_sys();   // acquire side: the other warps' stores and atomics of this panel
       __syncwarp();
       const float4 v = __ldcg(reinterpret_cast<const float4*>(p.rowss_local + m * 128) + lane);
+      if (MC) {
+        multimem_st_f32x4(p.rowss_mc + m * 128 + lane * 4, v);
+      } else {
 #pragma unroll
-      for (int d = 1; d <= W; d++) st_relaxed_sys_f32x4(p.rowss[(p.rank + d) % W] + m * 128 + lane * 4, v);
+        for (int d = 1; d <= W; d++) st_relaxed_sys_f32x4(p.rowss[(p.rank + d) % W] + m * 128 + lane * 4, v);
+      }
       __syncwarp();
       if (lane == 0) {
         fence_acq_rel_sys();   // x (all warps, through the arrival chain) and the row sums before the flags
+        if (MC) {
+          multimem_st_release_b32(p.panel_flag_mc + m, epoch);
+        } else {
 #pragma unroll
-        for (int d = 1; d <= W; d++) st_relaxed_sys(p.panel_flag[(p.rank + d) % W] + m, epoch);
+          for (int d = 1; d <= W; d++) st_relaxed_sys(p.panel_flag[(p.rank + d) % W] + m, epoch);
+        }
         if (p.trace) p.trace[m] = globaltimer();
       }
       __syncwarp();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ NVLS known-answer probes
+__global__ void mm_red_u32_kernel(unsigned* mc, int n, unsigned v) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) multimem_red_add_u32(mc + i, v);
+}
+__global__ void mm_red_f32_kernel(float* mc, const float* src, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) multimem_red_add_f32(mc + i, src[i]);
+}
+__global__ void mm_st_bf16_kernel(uint4* mc, const uint4* src, int n16) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) multimem_st_v4(mc + i, src[i]);
+}
+__global__ void mm_ld_reduce_bf16_kernel(const uint4* mc, uint4* out, int n16) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) out[i] = multimem_ld_reduce_bf16x8(mc + i);
+}
+// Ordering stress for the reducer's publish sequence: one block per slot.  In iteration `it` the slot's writer (rank
+// slot % world) broadcasts 512 bytes of payload with multimem.st, fences, and raises the slot's flag on every rank with a
+// releasing multimem.st; every rank (the writer too) waits for its local flag, checks that the payload it sees is the
+// one of this iteration, and acknowledges with a multimem reduction the writer waits for before it writes again.
+// Every wait is bounded; `result[0]` counts stale payload words, `result[1]` is set when a wait gave up.
+__global__ void __launch_bounds__(32) mm_order_stress_kernel(uint4* data_mc, const uint4* data_local, int* flag_mc, const int* flag_local,
+                                                             unsigned* ack_mc, const unsigned* ack_local, int rank, int world, int iters,
+                                                             int* result, long long limit_ns) {
+  const int slot = blockIdx.x, lane = threadIdx.x;
+  const bool writer = slot % world == rank;
+  for (int it = 1; it <= iters; it++) {
+    int seen;
+    if (writer) {
+      const unsigned v = static_cast<unsigned>(it) * 0x10001u + static_cast<unsigned>(slot);
+      multimem_st_v4(data_mc + slot * 32 + lane, make_uint4(v, v, v, v));
+      __syncwarp();
+      if (lane == 0) { fence_acq_rel_sys(); multimem_st_release_b32(flag_mc + slot, it); }
+    }
+    int ok = 1;
+    if (lane == 0) ok = spin_acquire_sys(flag_local + slot, PredGe{it}, limit_ns, seen) ? 1 : 0;
+    if (!__shfl_sync(0xffffffffu, ok, 0)) { if (lane == 0) atomicExch(result + 1, 1); return; }
+    const unsigned want = static_cast<unsigned>(it) * 0x10001u + static_cast<unsigned>(slot);
+    const uint4 got = __ldcg(data_local + slot * 32 + lane);
+    int bad = (got.x != want) + (got.y != want) + (got.z != want) + (got.w != want);
+    if (bad) atomicAdd(result, bad);
+    __syncwarp();
+    if (lane == 0) { fence_acq_rel_sys(); multimem_red_release_add_u32(ack_mc + slot, 1u); }
+    if (writer) {
+      if (lane == 0) ok = spin_acquire_sys(reinterpret_cast<const int*>(ack_local) + slot, PredGe{it * world}, limit_ns, seen) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, ok, 0)) { if (lane == 0) atomicExch(result + 1, 1); return; }
     }
   }
 }

@@ -101,7 +101,7 @@ class TpReduceArgs(C.Structure):
                 ("resid", C.c_void_p), ("peer_x", C.c_void_p * MAX_WORLD), ("peer_rowss", C.c_void_p * MAX_WORLD),
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("unit_ctr", C.c_void_p), ("trace", C.c_void_p),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p)]
 
 
 _SIGS = {
@@ -134,6 +134,12 @@ _SIGS = {
     "ctapp_tp_reduce": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_reduce_noalloc": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "ctapp_mm_red_u32": (C.c_int, [C.c_void_p, C.c_int, C.c_uint, C.c_int, C.c_void_p]),
+    "ctapp_mm_red_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "ctapp_mm_st_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "ctapp_mm_ld_reduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "ctapp_mm_order_stress": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                        C.c_void_p, C.c_int, C.c_void_p]),
     "ctapp_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "ctapp_kernel_info": (C.c_int, [C.c_int, C.c_char_p, C.c_int]),
 }
@@ -369,7 +375,7 @@ class Tp4Module:
     def tp4_reduce(self, M, rank, world, epoch, raster, blocks, tile_cnt, partials_mc=0, x_mc=0, resid=None, rowss_mc=0, panel_cnt_mc=0,
                    unicast=0, peer_partials=(), peer_x=(), version=5, epoch_dev=None, inbox_ptrs=(), peer_rowss=(), peer_panel_flag=(),
                    rowss_local=0, panel_done=0, panels_per_owner=0, threads=1024, variant=1, swz=1, rows=2, red_trace=0, dsmem=0, stages=0,
-                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None):
+                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
         if version != 5:
             raise RuntimeError(f"tp4_reduce: version {version} is not available in this build (5)")
         a = TpReduceArgs()
@@ -382,8 +388,36 @@ class Tp4Module:
         a.rowss_local, a.panel_done = _ptr(rowss_local), _ptr(panel_done)
         a.panels_per_owner, a.tail_cols = int(panels_per_owner), int(tail_cols)
         a.unit_ctr, a.trace, a.status = _ptr(unit_ctr), _ptr(red_trace), _ptr(status)
+        a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
+
+    # ---- NVLS probes (reference csrc/gemm_tp4.cu:393-502); ``mc`` is a multicast device address (int)
+    def mm_red_u32(self, mc, n, v):
+        dev = torch.cuda.current_device()
+        _check(self.lib.ctapp_mm_red_u32(_ptr(mc), int(n), int(v), dev, _stream(dev)))
+
+    def mm_red_f32(self, mc, src):
+        dev = src.device.index
+        _check(self.lib.ctapp_mm_red_f32(_ptr(mc), _ptr(src), src.numel(), dev, _stream(dev)))
+
+    def mm_st_bf16(self, mc, src):
+        dev = src.device.index
+        _check(self.lib.ctapp_mm_st_bf16(_ptr(mc), _ptr(src), src.numel(), dev, _stream(dev)))
+
+    def mm_ld_reduce_bf16(self, mc, out):
+        dev = out.device.index
+        _check(self.lib.ctapp_mm_ld_reduce_bf16(_ptr(mc), _ptr(out), out.numel(), dev, _stream(dev)))
+
+    def mm_order_stress(self, data_mc, data, flag_mc, flag, ack_mc, ack, rank, world, iters, slots):
+        """Returns (stale payload words seen, 1 if a wait gave up else 0); synchronises the device."""
+        dev = data.device.index
+        res = torch.zeros(2, dtype=torch.int32, device=data.device)
+        _check(self.lib.ctapp_mm_order_stress(_ptr(data_mc), _ptr(data), _ptr(flag_mc), _ptr(flag), _ptr(ack_mc), _ptr(ack), int(rank), int(world),
+                                              int(iters), int(slots), _ptr(res), dev, _stream(dev)))
+        torch.cuda.synchronize(dev)
+        r = res.cpu().tolist()
+        return r[0], r[1]
 
     def tp4_reduce_noalloc(self, M, rank, world, epoch, blocks, tile_flags, resid=None, peer_x=(), epoch_dev=None, inbox_ptrs=(),
                            peer_rowss=(), peer_panel_flag=(), panels_per_owner=0, threads=1024, tail_cols=0, n1=8192, status=None):

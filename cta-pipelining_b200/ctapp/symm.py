@@ -104,16 +104,17 @@ class LocalGroup:
             torch.cuda.synchronize(d)
 
 
-def symm_empty(shape, dtype, dev, group, rank=None):
+def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
     """-> (this rank's tensor, SymmHandle).  ``group``: a LocalGroup, or a torch.distributed group name / None for the
-    default process group.  Collective over the group in the multi-process case."""
+    default process group.  Collective over the group in the multi-process case.  ``multicast``: the buffer must also
+    have a multicast address (NVLS): only torch's symmetric memory provides one."""
     if isinstance(group, LocalGroup):
         return group.alloc(shape, dtype, rank)
     import torch.distributed as dist
     if not dist.is_initialized() or dist.get_world_size() == 1:
         t = torch.zeros(_shape(shape), dtype=dtype, device=dev)
         return t, SymmHandle([t.data_ptr()], 0, keep=t)
-    if os.environ.get("CTAPP_SYMM", "ipc") == "torch":
+    if multicast or os.environ.get("CTAPP_SYMM", "ipc") == "torch":
         import torch.distributed._symmetric_memory as symm_mem
         t = symm_mem.empty(*_shape(shape), dtype=dtype, device=dev)
         hdl = symm_mem.rendezvous(t, group if isinstance(group, str) else dist.group.WORLD.group_name)

@@ -38,9 +38,9 @@ K_FFN = 28672
 N2 = 10240         # fused QKV width
 
 
-def _symm(shape, dtype, dev, group_name, rank=None):
+def _symm(shape, dtype, dev, group_name, rank=None, multicast=False):
     """(tensor, handle with ``buffer_ptrs`` / ``multicast_ptr``): reference ctapp/tp4.py:31-35."""
-    return symm_empty(shape, dtype, dev, group_name, rank)
+    return symm_empty(shape, dtype, dev, group_name, rank, multicast)
 
 
 def shard_weights(Wdown, Wqkv, gamma, rank, world):
@@ -72,9 +72,11 @@ class CtappBoundary:
     ``SMs - R`` SMs.  All flags are epoch values, so one instance sized ``max_M`` serves every M <= max_M with
     M % 128 == 0; ``out`` and ``x()`` are views of the first M rows.
 
-    protocol: "v5" (default here).  True / "v3" name the reference's NVLS-multimem protocol, which this build does not
-    have; they select the same unicast protocol and log a note.  False = the two GEMMs alone (no exchange, no residual):
-    the floor the protocol is measured against.
+    protocol: "v5" (default here) = unicast pushes; True / "v3" = NVLS variant: the same panel-ownership protocol, but the owner
+    reducer pushes x, the row sums and the panel flags with ``multimem.st`` on multicast addresses, so each row leaves the
+    owner once and the NVSwitch replicates it (needs one process per GPU, >= 2 ranks, torch symmetric memory with multicast;
+    falls back to unicast with a warning otherwise).  False = the two GEMMs alone (no exchange, no residual): the floor the
+    protocol is measured against.
     fusion: "none" = reducer on a side stream, consumer after the producer in stream order;
             "pdl"  = as "none" and the consumer is launched as the producer's programmatic dependent, so its CTAs start
                      as producer CTAs retire (the per-panel flags carry the data dependency);
@@ -95,8 +97,11 @@ class CtappBoundary:
         assert M % 128 == 0 and n1 % 256 == 0, (M, n1)
         assert protocol in (True, False, "v3", "v5"), protocol
         assert world in (1, 2, 4, 8), f"world {world} is not supported"
-        if protocol in (True, "v3"):
-            log.info("ctapp: the NVLS multimem protocol is not part of this build; using the unicast panel-ownership protocol")
+        # True / "v3": NVLS variant -- the owner reducer pushes x, row sums and panel flags with multimem stores on multicast
+        # addresses (replicated inside the NVSwitch); needs one process per GPU, world >= 2 and multicast support
+        self.nvls = protocol in (True, "v3") and world >= 2 and not isinstance(group_name, LocalGroup)
+        if protocol in (True, "v3") and not self.nvls:
+            log.warning("ctapp: NVLS needs one process per GPU and at least 2 ranks; using unicast pushes")
         assert fusion in ("none", "pdl", "serial"), f"fusion {fusion!r} is not available in this build (none | pdl | serial)"
         assert red_variant == 1, "only the warp-per-unit reducer (variant 1) exists in this build"
         assert qkv_tile in (256, 128)
@@ -124,13 +129,19 @@ class CtappBoundary:
         with torch.cuda.device(dev):
             self.ext.preload(dev.index)
             self.ppo = ppo = -(-(max_M // 128) // world)            # panels per owner (ceil)
-            sy = lambda shape, dt: _symm(shape, dt, dev, group_name, rank)  # noqa: E731
+            sy = lambda shape, dt, mc=False: _symm(shape, dt, dev, group_name, rank, mc and self.nvls)  # noqa: E731
             self.inbox, hi = sy((world, ppo * 128, n1), DTYPE)       # this rank's inbox; slot s = source rank s
             self.tile_flags, ht = sy((world, ppo, tn), torch.int32)
-            self.panel_flag, hp = sy((max_M // 128,), torch.int32)
-            self.rowss, hr = sy((2, max_M), torch.float32)           # by epoch parity
-            self.xbuf, hx0 = sy((max_M, n1), DTYPE)
-            self.xbuf1, hx1 = sy((max_M, n1), DTYPE)
+            self.panel_flag, hp = sy((max_M // 128,), torch.int32, True)
+            self.rowss, hr = sy((2, max_M), torch.float32, True)     # by epoch parity
+            self.xbuf, hx0 = sy((max_M, n1), DTYPE, True)
+            self.xbuf1, hx1 = sy((max_M, n1), DTYPE, True)
+            if self.nvls and not (hp.multicast_ptr and hr.multicast_ptr and hx0.multicast_ptr and hx1.multicast_ptr):
+                log.warning("ctapp: no multicast address on this system; using unicast pushes")
+                self.nvls = False
+            self._x_mc = [hx0.multicast_ptr, hx1.multicast_ptr] if self.nvls else [0, 0]
+            self._rowss_mc = [hr.multicast_ptr + par * max_M * 4 for par in (0, 1)] if self.nvls else [0, 0]
+            self._pf_mc = hp.multicast_ptr if self.nvls else 0
             self._hdls = (hi, ht, hp, hr, hx0, hx1)
             self.xbufs = [self.xbuf, self.xbuf1]
             slot = ppo * 128 * n1 * 2                                 # bytes of one inbox slot
@@ -183,7 +194,8 @@ class CtappBoundary:
                             peer_rowss=self._peer_rowss[parity], peer_panel_flag=self._peer_pf, rowss_local=self.rowss_local,
                             panel_done=self.panel_done, panels_per_owner=self.ppo, threads=self.red_threads,
                             red_trace=self._tr(self.trace_red), unit_ctr=self.role_ctr[1:] if self.steal else 0,
-                            tail_cols=self._tail(M), n1=self.n1, status=self.status)
+                            tail_cols=self._tail(M), n1=self.n1, status=self.status, x_mc_ptr=self._x_mc[parity],
+                            rowss_mc_ptr=self._rowss_mc[parity], panel_flag_mc_ptr=self._pf_mc)
 
     def _down_v5(self, h_r, Wd, M):
         self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms,

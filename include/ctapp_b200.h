@@ -146,6 +146,11 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   int* unit_ctr;                            /* NULL = static unit assignment */
   unsigned long long* trace;
   int* status;
+  /* NVLS variant (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.st / multimem.red pushes): multicast addresses of the x
+   * buffer, the row-sum buffer and the panel flags; all NULL = unicast pushes to peer_x / peer_rowss / peer_panel_flag */
+  void* x_mc;
+  float* rowss_mc;
+  int* panel_flag_mc;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 
@@ -168,6 +173,17 @@ int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* args, int device, void* 
 
 /* epoch_dev[0] += 1; zero rowss_local[0:M], panel_done[0:M/128] and role_ctr[0:2].  gemm_tp4.cu:362-372 (tp4_step). */
 int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream);
+
+/* NVLS known-answer probes on a multicast address `mc` (csrc/gemm_tp4.cu:393-502: mm_red_u32, mm_red_f32, mm_st_bf16,
+ * mm_ld_reduce_bf16, mm_order_stress).  The ordering stress runs the reducer's publish sequence (multimem.st payload,
+ * fence, releasing multimem.st flag) `iters` times per slot with bounded waits; result[0] = stale payload words seen,
+ * result[1] != 0 = a wait gave up. */
+int ctapp_mm_red_u32(void* mc, int n, unsigned v, int device, void* stream);
+int ctapp_mm_red_f32(void* mc, const float* src, int n, int device, void* stream);
+int ctapp_mm_st_bf16(void* mc, const void* src, int n, int device, void* stream);
+int ctapp_mm_ld_reduce_bf16(const void* mc, void* out, int n, int device, void* stream);
+int ctapp_mm_order_stress(void* data_mc, const void* data_local, int* flag_mc, const int* flag_local, unsigned* ack_mc,
+                          const unsigned* ack_local, int rank, int world, int iters, int slots, int* result, int device, void* stream);
 
 /* Comparison baseline only: x = a + resid (bf16), y = rmsnorm(x) * gamma, one pass (the fused add+RMSNorm a serving
  * stack runs after an all-reduce).  No counterpart in the reference (it used eager torch, ctapp/tp4.py:47-50). */

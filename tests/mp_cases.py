@@ -1,0 +1,111 @@
+"""Per-rank bodies of the multi-process GPU tests (one process per GPU, spawned through ``ctapp.tp4.launch``).  Each returns
+a list of failure strings (empty = pass)."""
+import torch
+import torch.distributed as dist
+
+
+def _sync(dev):
+    from ctapp import tp4
+    torch.cuda.synchronize(dev)
+    tp4.barrier()
+
+
+def nvls_probes(rank, world, dev, gn):
+    """Known answers for the multimem operations the NVLS variant uses (reference tests/test_tp4.py:44-107)."""
+    from ctapp.ext import load_tp4
+    from ctapp.symm import symm_empty
+    ext = load_tp4()
+    fails = []
+    buf, h = symm_empty((4096,), torch.int32, dev, gn, rank, multicast=True)
+    if not h.multicast_ptr:
+        return ["SKIP: no multicast address on this system"]
+    for n in (1, 100, 4096):
+        buf.zero_(); _sync(dev)
+        ext.mm_red_u32(h.multicast_ptr, n, 3); _sync(dev)
+        b = buf.cpu()
+        if not (bool((b[:n] == 3 * world).all()) and bool((b[n:] == 0).all())):
+            fails.append(f"mm_red_u32 n={n}")
+    n = 8192
+    fb, fh = symm_empty((n,), torch.float32, dev, gn, rank, multicast=True)
+    srcs = [torch.randn(n, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    fb.zero_(); _sync(dev)
+    ext.mm_red_f32(fh.multicast_ptr, srcs[rank].to(dev)); _sync(dev)
+    if (fb.cpu() - sum(srcs)).abs().max().item() >= 1e-4:
+        fails.append("mm_red_f32")
+    bb, bh = symm_empty((n,), torch.bfloat16, dev, gn, rank, multicast=True)
+    bb.zero_(); _sync(dev)
+    src = torch.randn(n, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+    if rank == 0:
+        ext.mm_st_bf16(bh.multicast_ptr, src.to(dev))
+    _sync(dev)
+    if not torch.equal(bb.cpu(), src):
+        fails.append("mm_st_bf16 broadcast")
+    n = 65536
+    lb, lh = symm_empty((n,), torch.bfloat16, dev, gn, rank, multicast=True)
+    datas = [(torch.randn(n, generator=torch.Generator().manual_seed(200 + r)) * 0.1).to(torch.bfloat16) for r in range(world)]
+    lb.copy_(datas[rank]); _sync(dev)
+    out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    ext.mm_ld_reduce_bf16(lh.multicast_ptr, out); _sync(dev)
+    exp = sum(d.float() for d in datas).to(torch.bfloat16)
+    mism = (out.cpu() != exp).sum().item()
+    if mism > n * 1e-4:
+        fails.append(f"mm_ld_reduce_bf16: {mism} mismatches of {n}")
+    if world >= 3:      # 256 + 1 + 1 (+...) only survives when the switch accumulates in fp32
+        vals = [256.0] + [1.0] * (world - 1)
+        lb.fill_(vals[rank]); _sync(dev)
+        ext.mm_ld_reduce_bf16(lh.multicast_ptr, out); _sync(dev)
+        if not bool((out.cpu() == torch.tensor(sum(vals)).to(torch.bfloat16)).all()):
+            fails.append("mm_ld_reduce_bf16 does not accumulate in fp32")
+    slots, iters = 64, 500
+    db, dh = symm_empty((slots * 32 * 8,), torch.bfloat16, dev, gn, rank, multicast=True)
+    fl, fh2 = symm_empty((slots,), torch.int32, dev, gn, rank, multicast=True)
+    ak, ah = symm_empty((slots,), torch.int32, dev, gn, rank, multicast=True)
+    db.zero_(); fl.zero_(); ak.zero_(); _sync(dev)
+    stale, gave_up = ext.mm_order_stress(dh.multicast_ptr, db, fh2.multicast_ptr, fl, ah.multicast_ptr, ak, rank, world, iters, slots)
+    _sync(dev)
+    if stale or gave_up:
+        fails.append(f"mm_order_stress: {stale} stale words, gave_up={gave_up}")
+    return fails
+
+
+def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N2_):
+    """The boundary with one process per GPU against the CPU oracle; also x identical on every rank and flags == epoch."""
+    import sys, os
+    from ctapp import tp4
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    from oracle import boundary as ob
+    from oracle import chain as oc
+    fails = []
+    Kr, N2r = K // world, N2_ // world
+    max_M = max(Ms)
+    bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair)
+    if protocol == "v3" and not bd.nvls:
+        return ["SKIP: no multicast address on this system"]
+    for it, M in enumerate(Ms):
+        Wd, gamma, Wq = ob.make_weights(seed=1 + it, K=K, N2_=N2_, n1=n1)
+        wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, rank, world)
+        h, resid = ob.make_inputs(M, seed=40 + it, K=K, n1=n1)
+        out = bd.forward(h[:, rank * Kr:(rank + 1) * Kr].contiguous().to(dev), resid.to(dev), wd.to(dev), wqf.to(dev))
+        bd.check()
+        x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, world)
+        x = bd.x().cpu()
+        ulp = lambda a, b: ((a.view(torch.int16).int() - b.view(torch.int16).int()).abs() <= 1).float().mean().item()  # noqa: E731
+        if ulp(x, x_model) < 0.99:
+            fails.append(f"M={M}: x within one ulp only {ulp(x, x_model):.4f}")
+        o = out.cpu()
+        om = out_model[:, rank * N2r:(rank + 1) * N2r]
+        mx, mean = oc.error_stats(o, om)
+        if not (mx <= 2e-2 and mean <= 1e-3 and ulp(o, om) >= 0.98):
+            fails.append(f"M={M}: out max {mx:.3e} mean {mean:.3e} ulp {ulp(o, om):.4f}")
+        bits = [None] * world
+        dist.all_gather_object(bits, int(x.view(torch.int16).to(torch.int64).sum().item()), group=tp4.GLOO)
+        if len(set(bits)) != 1:
+            fails.append(f"M={M}: x differs between ranks")
+        P = M // 128
+        Pr = ob.panels_owned(M, rank, world)
+        if not bool((bd.tile_flags[:, :Pr, :].cpu() == bd.epoch).all()) or not bool((bd.panel_flag[:P].cpu() == bd.epoch).all()):
+            fails.append(f"M={M}: flags != epoch {bd.epoch}")
+        _sync(dev)
+    return fails

@@ -104,6 +104,16 @@ class LocalGroup:
             torch.cuda.synchronize(d)
 
 
+def _process_group(group):
+    """torch.distributed group object for a group name (None = the default group)."""
+    import torch.distributed as dist
+    if group is None or not dist.is_initialized():
+        return None
+    if isinstance(group, str):
+        return dist.distributed_c10d._resolve_process_group(group)
+    return group
+
+
 def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
     """-> (this rank's tensor, SymmHandle).  ``group``: a LocalGroup, or a torch.distributed group name / None for the
     default process group.  Collective over the group in the multi-process case.  ``multicast``: the buffer must also
@@ -111,7 +121,7 @@ def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
     if isinstance(group, LocalGroup):
         return group.alloc(shape, dtype, rank)
     import torch.distributed as dist
-    if not dist.is_initialized() or dist.get_world_size() == 1:
+    if not dist.is_initialized() or dist.get_world_size(_process_group(group)) == 1:
         t = torch.zeros(_shape(shape), dtype=dtype, device=dev)
         return t, SymmHandle([t.data_ptr()], 0, keep=t)
     if multicast or os.environ.get("CTAPP_SYMM", "ipc") == "torch":
@@ -128,9 +138,10 @@ def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
     torch.cuda.synchronize(device)
     handle = C.create_string_buffer(64)
     _check(lib().ctapp_ipc_get_handle(C.c_void_p(alloc.ptr), handle, device))
-    me, world = dist.get_rank(), dist.get_world_size()
+    pg = _process_group(group)
+    me, world = dist.get_rank(pg), dist.get_world_size(pg)
     gathered = [None] * world
-    dist.all_gather_object(gathered, bytes(handle.raw))
+    dist.all_gather_object(gathered, bytes(handle.raw), group=pg)
     ptrs, opened = [], []
     for r in range(world):
         if r == me:

@@ -362,8 +362,11 @@ def forward_lockstep(bds, h_rs, resids, Wds, Wqs):
 def _group_barrier(group):
     if isinstance(group, LocalGroup):
         group.barrier()
-    elif dist.is_initialized() and dist.get_world_size() > 1:
-        dist.barrier()
+    elif dist.is_initialized():
+        from ctapp.symm import _process_group
+        pg = _process_group(group)
+        if dist.get_world_size(pg) > 1:
+            dist.barrier(group=pg)
 
 
 class CtappBoundaryPool:
@@ -392,7 +395,7 @@ class CtappBoundaryPool:
         bd = self._inst.get(self.max_M)
         if bd is None:
             bd = CtappBoundary(self.max_M, self.Kr, self.N2r, self.rank, self.world, self.gn, self.dev, R=self.R,
-                               qkv_raster=self.qkv_raster, qkv_swizzle=self.qkv_swizzle, protocol="v5", max_M=self.max_M, **self.v5kw)
+                               qkv_raster=self.qkv_raster, qkv_swizzle=self.qkv_swizzle, protocol=self.protocol, max_M=self.max_M, **self.v5kw)
             self._inst[self.max_M] = bd
         return bd
 

@@ -46,10 +46,13 @@ def nvls_probes(rank, world, dev, gn):
     lb.copy_(datas[rank]); _sync(dev)
     out = torch.empty(n, dtype=torch.bfloat16, device=dev)
     ext.mm_ld_reduce_bf16(lh.multicast_ptr, out); _sync(dev)
+    # the in-switch sum is accumulated in fp32 (proved below with 3+ ranks) but its final conversion to bf16 is not round to
+    # nearest even on this hardware: about one result in five is the neighbouring bf16.  One ulp is the contract checked here
+    # (the boundary itself never uses ld_reduce: the owner reducer adds in registers and rounds once, to nearest even).
     exp = sum(d.float() for d in datas).to(torch.bfloat16)
-    mism = (out.cpu() != exp).sum().item()
-    if mism > n * 1e-4:
-        fails.append(f"mm_ld_reduce_bf16: {mism} mismatches of {n}")
+    d_ulp = (out.cpu().view(torch.int16).int() - exp.view(torch.int16).int()).abs()
+    if int(d_ulp.max()) > 1:
+        fails.append(f"mm_ld_reduce_bf16: off by {int(d_ulp.max())} ulp")
     if world >= 3:      # 256 + 1 + 1 (+...) only survives when the switch accumulates in fp32
         vals = [256.0] + [1.0] * (world - 1)
         lb.fill_(vals[rank]); _sync(dev)

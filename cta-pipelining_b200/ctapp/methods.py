@@ -1,6 +1,7 @@
-"""The methods the chain is compared with, all driven from one process on devices 0 and 1 (mirrors reference
-ctapp/methods.py:27-141): one GPU doing both layers (the "ideal" is half of it), micro-batching with peer copies, tensor
-parallelism with an NCCL all-reduce, and the CTA-pipelined chain.  Each has ``prepare()`` (untimed) and ``enqueue()``."""
+"""What the chain is compared with, all driven from one process on devices 0 and 1: one GPU doing both layers (half of it
+is the chain's ideal), micro-batching with peer copies, tensor parallelism with an NCCL all-reduce, and the CTA-pipelined
+chain itself.  Same class names and constructor arguments as reference ctapp/methods.py:27-141; every method has
+``prepare()`` (untimed) and ``enqueue()`` (timed) and ``result()``."""
 from __future__ import annotations
 
 import torch
@@ -9,18 +10,18 @@ from ctapp.ext import load
 from ctapp.pipeline import Pipeline
 
 BF = torch.bfloat16
-_ext = None
 
 
 def ext():
-    global _ext
-    if _ext is None:
-        _ext = load()
-    return _ext
+    return load()
 
 
 def dev(i):
     return torch.device("cuda", i)
+
+
+def _out(M, W, device):
+    return torch.empty(M, W.shape[0], device=device, dtype=BF)
 
 
 class Base:
@@ -32,17 +33,19 @@ class Base:
 
 
 class OneGpuCublas(Base):
-    """Both layers on device 0 with the library GEMM; half of its time is the chain's ideal (one GEMM's time)."""
+    """Both layers on device 0 with the library GEMM."""
 
     def __init__(self, M, X, W1, W2):
         self.X, self.W1, self.W2 = X, W1, W2
-        self.Y1 = torch.empty(M, W1.shape[0], device=dev(0), dtype=BF)
-        self.Y2 = torch.empty(M, W2.shape[0], device=dev(0), dtype=BF)
+        self.Y1, self.Y2 = _out(M, W1, dev(0)), _out(M, W2, dev(0))
+
+    def _mm(self, x, w, y):
+        torch.mm(x, w.t(), out=y)
 
     def enqueue(self):
         with torch.cuda.device(0):
-            torch.mm(self.X, self.W1.t(), out=self.Y1)
-            torch.mm(self.Y1, self.W2.t(), out=self.Y2)
+            self._mm(self.X, self.W1, self.Y1)
+            self._mm(self.Y1, self.W2, self.Y2)
 
 
 class OneGpuTma(OneGpuCublas):
@@ -52,45 +55,42 @@ class OneGpuTma(OneGpuCublas):
         super().__init__(M, X, W1, W2)
         self.cfg = cfg
 
-    def enqueue(self):
-        with torch.cuda.device(0):
-            ext().gemm_tma(self.X, self.W1, self.Y1, self.cfg)
-            ext().gemm_tma(self.Y1, self.W2, self.Y2, self.cfg)
+    def _mm(self, x, w, y):
+        ext().gemm_tma(x, w, y, self.cfg)
 
 
 class MicroBatchCublas(Base):
-    """Layer 1 on device 0 and layer 2 on device 1, M split into chunks: GEMM chunk i, copy it over, GEMM on the other side,
-    each on its own stream.  chunk == M is the plain sequential two-GPU pipeline."""
+    """Layer 1 on device 0, layer 2 on device 1, the M rows cut into chunks: compute chunk i, copy it across on a copy
+    stream, compute on the other side.  chunk == M is the plain sequential two-GPU pipeline."""
 
     def __init__(self, M, X, W1, W2, chunk):
-        ext().enable_peer_access(0, 1); ext().enable_peer_access(1, 0)
-        self.M, self.chunk, self.X, self.W1, self.W2 = M, min(chunk, M), X, W1, W2
-        N1, N2 = W1.shape[0], W2.shape[0]
-        self.Y1a = torch.empty(M, N1, device=dev(0), dtype=BF)
-        self.Y1b = torch.empty(M, N1, device=dev(1), dtype=BF)
-        self.Y2 = torch.empty(M, N2, device=dev(1), dtype=BF)
-        self.sA, self.sB = torch.cuda.current_stream(0), torch.cuda.current_stream(1)
+        ext().enable_peer_access(0, 1); ext().enable_peer_access(1, 0)     # otherwise the copies bounce through the host
+        self.X, self.W1, self.W2 = X, W1, W2
+        step = min(chunk, M)
+        self.slices = [slice(a, min(a + step, M)) for a in range(0, M, step)]
+        self.Y1a, self.Y1b, self.Y2 = _out(M, W1, dev(0)), _out(M, W1, dev(1)), _out(M, W2, dev(1))
+        self.compute0, self.compute1 = torch.cuda.current_stream(0), torch.cuda.current_stream(1)
         with torch.cuda.device(0):
-            self.sC = torch.cuda.Stream()
-        self.n = -(-M // self.chunk)
-        self.evA = [torch.cuda.Event() for _ in range(self.n)]
-        self.evC = [torch.cuda.Event() for _ in range(self.n)]
+            self.copier = torch.cuda.Stream()
+        self.done0 = [torch.cuda.Event() for _ in self.slices]
+        self.copied = [torch.cuda.Event() for _ in self.slices]
 
     def gemm(self, x, w, y):
         torch.mm(x, w.t(), out=y)
 
     def enqueue(self):
-        c = self.chunk
-        for i in range(self.n):
-            sl = slice(i * c, min((i + 1) * c, self.M))
+        for i, rows in enumerate(self.slices):
             with torch.cuda.device(0):
-                with torch.cuda.stream(self.sA):
-                    self.gemm(self.X[sl], self.W1, self.Y1a[sl]); self.evA[i].record(self.sA)
-                with torch.cuda.stream(self.sC):
-                    self.sC.wait_event(self.evA[i]); ext().peer_copy(self.Y1b[sl], self.Y1a[sl]); self.evC[i].record(self.sC)
-            with torch.cuda.device(1), torch.cuda.stream(self.sB):
-                self.sB.wait_event(self.evC[i])
-                self.gemm(self.Y1b[sl], self.W2, self.Y2[sl])
+                with torch.cuda.stream(self.compute0):
+                    self.gemm(self.X[rows], self.W1, self.Y1a[rows])
+                    self.done0[i].record(self.compute0)
+                with torch.cuda.stream(self.copier):
+                    self.copier.wait_event(self.done0[i])
+                    ext().peer_copy(self.Y1b[rows], self.Y1a[rows])
+                    self.copied[i].record(self.copier)
+            with torch.cuda.device(1), torch.cuda.stream(self.compute1):
+                self.compute1.wait_event(self.copied[i])
+                self.gemm(self.Y1b[rows], self.W2, self.Y2[rows])
 
 
 class MicroBatchTma(MicroBatchCublas):
@@ -103,20 +103,20 @@ class MicroBatchTma(MicroBatchCublas):
 
 
 class TensorParallel2(Base):
-    """Megatron split over two GPUs: W1 by rows, W2 by columns, all-reduce of the (M, N2) partial sums (single-process
-    NCCL).  X is replicated."""
+    """Megatron split over two GPUs: W1 by rows, W2 by columns, all-reduce of the (M, N2) partial sums with single-process
+    NCCL.  X is replicated."""
 
     def __init__(self, M, X, W1, W2):
-        N1, N2 = W1.shape[0], W2.shape[0]
-        h = N1 // 2
+        half = W1.shape[0] // 2
         W2 = W2.to(dev(0))
+        cut = [slice(g * half, (g + 1) * half) for g in range(2)]
         self.X = [X, X.to(dev(1))]
-        self.W1 = [W1[g * h:(g + 1) * h].contiguous().to(dev(g)) for g in range(2)]
-        self.W2 = [W2[:, g * h:(g + 1) * h].contiguous().to(dev(g)) for g in range(2)]
-        self.Y1 = [torch.empty(M, h, device=dev(g), dtype=BF) for g in range(2)]
-        self.P = [torch.empty(M, N2, device=dev(g), dtype=BF) for g in range(2)]
-        self.s = [torch.cuda.current_stream(g) for g in range(2)]
-        for _ in range(3):
+        self.W1 = [W1[cut[g]].contiguous().to(dev(g)) for g in range(2)]
+        self.W2 = [W2[:, cut[g]].contiguous().to(dev(g)) for g in range(2)]
+        self.Y1 = [_out(M, self.W1[g], dev(g)) for g in range(2)]
+        self.P = [_out(M, W2, dev(g)) for g in range(2)]
+        self.streams = [torch.cuda.current_stream(g) for g in range(2)]
+        for _ in range(3):      # NCCL communicator set-up happens on first use
             self.enqueue()
         torch.cuda.synchronize(0); torch.cuda.synchronize(1)
 
@@ -125,7 +125,7 @@ class TensorParallel2(Base):
             with torch.cuda.device(g):
                 torch.mm(self.X[g], self.W1[g].t(), out=self.Y1[g])
                 torch.mm(self.Y1[g], self.W2[g].t(), out=self.P[g])
-        torch.cuda.nccl.all_reduce(self.P, streams=self.s)
+        torch.cuda.nccl.all_reduce(self.P, streams=self.streams)
 
     def result(self):
         return self.P[1]

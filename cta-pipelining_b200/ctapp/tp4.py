@@ -488,8 +488,11 @@ def make_weights(dev, seed=0, K=K_FFN, N2_=N2, n1=N1):
     return Wd.to(dev), gamma.to(dev), Wq.to(dev)
 
 
-# --------------------------------------------------------------------------- process harness + timing
-GLOO = None
+# --------------------------------------------------------------------------- process harness + timing (ctapp/harness.py)
+from ctapp import harness as _harness  # noqa: E402
+from ctapp.harness import launch, time_one_gpu  # noqa: E402,F401
+
+GLOO = None      # the gloo side group of this process (set by ``launch`` workers, or by the caller)
 
 
 def barrier():
@@ -499,115 +502,4 @@ def barrier():
 def time_step(step, dev, iters, warmup):
     """(per-step median ms with barrier + sync before each call, back-to-back mean ms), both max over ranks
     (reference ctapp/tp4.py:696-723)."""
-    for _ in range(warmup):
-        step()
-    torch.cuda.synchronize(dev)
-    barrier()
-    times = []
-    for _ in range(iters):
-        barrier()
-        torch.cuda.synchronize(dev)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        step()
-        b.record()
-        torch.cuda.synchronize(dev)
-        times.append(a.elapsed_time(b))
-    ps = statistics.median(times)
-    barrier()
-    torch.cuda.synchronize(dev)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        step()
-    b.record()
-    torch.cuda.synchronize(dev)
-    t = torch.tensor([ps, a.elapsed_time(b) / iters], dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=GLOO)
-    return t.tolist()
-
-
-def time_one_gpu(fn, dev, iters, warmup):
-    for _ in range(warmup):
-        fn()
-    times = []
-    for _ in range(iters):
-        torch.cuda.synchronize(dev)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize(dev)
-        times.append(a.elapsed_time(b))
-    return statistics.median(times)
-
-
-def _entry(rank, world, port, fn, args, queue, backend):
-    global GLOO
-    os.environ.setdefault("TORCH_NCCL_ENABLE_MONITORING", "0")
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    for p in (os.path.dirname(os.path.dirname(os.path.abspath(__file__))),):
-        if p not in sys.path:
-            sys.path.insert(0, p)
-    code = 0
-    try:
-        if backend == "nccl":
-            dev = torch.device("cuda", rank)
-            torch.cuda.set_device(dev)
-            dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
-            GLOO = dist.new_group(backend="gloo")
-        else:
-            dev = torch.device("cpu")
-            dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
-            GLOO = dist.group.WORLD
-        res = fn(rank, world, dev, dist.group.WORLD.group_name, *args)
-        if backend == "nccl":
-            torch.cuda.synchronize(dev)
-        barrier()
-        queue.put((rank, "ok", res))
-    except BaseException:  # noqa: BLE001
-        traceback.print_exc()
-        queue.put((rank, "err", traceback.format_exc()))
-        code = 1
-    sys.stdout.flush()
-    sys.stderr.flush()
-    queue.close()
-    queue.join_thread()
-    os._exit(code)  # skip process-group teardown (it can block when a peer has already gone)
-
-
-def launch(fn, world, port, *args, backend="nccl", grace_s=10.0):
-    """Run fn(rank, world, dev, group_name, *args) in ``world`` processes (one per GPU; backend "gloo" runs them on the
-    CPU); returns (per-rank results, bad).  A rank that dies or raises makes ``bad`` true and its result None; the
-    others are not left waiting (reference ctapp/tp4.py:767-790)."""
-    import queue as _q
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, backend)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results, got = [None] * world, 0
-    failed_at = None
-    while got < world:
-        try:
-            r, st, res = q.get(timeout=1)
-            results[r] = res if st == "ok" else None
-            got += 1
-            if st != "ok" and failed_at is None:
-                failed_at = time.time()
-        except _q.Empty:
-            if all(not p.is_alive() for p in procs):
-                break
-            if failed_at is None and any(p.exitcode not in (None, 0) for p in procs):
-                failed_at = time.time()
-        # a rank has failed: the others may be blocked in a collective with it; give them a grace period, then stop them
-        if failed_at is not None and time.time() - failed_at > grace_s:
-            break
-    for p in procs:
-        p.join(timeout=0.5 if failed_at is not None else 30)
-        if p.is_alive():
-            p.kill()
-            p.join(timeout=5)
-    bad = got < world or any(r is None for r in results)
-    return results, bad
+    return _harness.time_step(step, dev, iters, warmup, GLOO)

@@ -172,7 +172,7 @@ def run_boundary(args, rank, world, local_rank):
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
     iters, warm = max(args.steps, 10), max(args.warmup, 3)
     res = {}
-    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol="v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
@@ -192,7 +192,7 @@ def run_boundary(args, rank, world, local_rank):
         burst, sustained, kind = peaks()
         b2b = res["ctapp"][1]
         print(json.dumps({"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
-                          "n_gpus": t, "fusion": args.fusion, "R": bd.R, "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
+                          "n_gpus": t, "fusion": args.fusion, "R": bd.R, "push": "nvls multimem" if bd.nvls else "unicast", "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
                           "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
                           "tflops_per_gpu_b2b": flops / (b2b * 1e-3) / 1e12, "frac_of_burst_peak": flops / (b2b * 1e-3) / 1e12 / burst,
                           "out_rel_vs_stock": rel, "iters": iters}), flush=True)
@@ -211,6 +211,7 @@ def main():
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
+    ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
     ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")
     args = ap.parse_args()

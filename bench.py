@@ -157,7 +157,7 @@ def run_boundary(args, rank, world, local_rank):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29577")
         dist.init_process_group("gloo", rank=0, world_size=1)
     tp4.GLOO = dist.new_group(backend="gloo")
-    M = args.m if args.m != 8192 else 4096
+    M = args.m
     t = world
     Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
     kfull = Kr * t
@@ -204,7 +204,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tokens", dest="m", type=int, default=8192, help="M, the number of token rows")
+    ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
@@ -215,6 +215,8 @@ def main():
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
     ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")
     args = ap.parse_args()
+    if args.m is None:
+        args.m = 4096 if args.workload == "boundary" and args.impl == "ours" else 8192
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

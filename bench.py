@@ -172,7 +172,7 @@ def run_boundary(args, rank, world, local_rank):
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
     iters, warm = max(args.steps, 10), max(args.warmup, 3)
     res = {}
-    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw, **(dict(red_variant=args.red_variant) if args.red_variant else {}))
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
@@ -198,6 +198,60 @@ def run_boundary(args, rank, world, local_rank):
                           "out_rel_vs_stock": rel, "iters": iters}), flush=True)
 
 
+def run_reducer(args, rank, world, local_rank):
+    """The owner reducer alone (every tile flag already raised): reads the t inbox slices + the residual of this rank's M/t
+    rows, writes x to every rank, publishes row sums and panel flags.  Bytes per rank with S = (M/t) * n1 * 2: HBM reads
+    (t + 1) * S, HBM writes t * S (its own copy + what the peers push), NVLink egress (t - 1) * S.  One JSON line on rank 0."""
+    import torch.distributed as dist
+    from ctapp import tp4
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29579")
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    tp4.GLOO = dist.new_group(backend="gloo")
+    M, t = args.m, world
+    out = {}
+    rv = dict(red_variant=args.red_variant) if args.red_variant else {}
+    resid = torch.randn(M, tp4.N1, device=dev).to(torch.bfloat16)
+    for R in ([args.R] if args.R else [4, 8, 16, 32]):
+        bd = tp4.CtappBoundary(M, 256, 256, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, R=R, **rv)
+        bd.inbox.normal_()
+        ext = bd.ext
+        times = []
+        for it in range(max(args.warmup, 3) + max(args.steps, 10)):
+            bd.epoch += 1
+            ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, M, bd.role_ctr)
+            bd.tile_flags.fill_(bd.epoch)                      # every producer tile "has arrived"
+            torch.cuda.synchronize(dev); tp4.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); bd._reduce_v5(M, resid, bd.epoch & 1); b.record()
+            torch.cuda.synchronize(dev); tp4.barrier()
+            if it >= max(args.warmup, 3):
+                times.append(a.elapsed_time(b))
+        bd.check()
+        assert bool((bd.panel_flag[:M // 128].cpu() == bd.epoch).all())
+        v = torch.tensor([statistics.median(times)], dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX, group=tp4.GLOO)
+        out[R] = float(v.item())
+        del bd
+    if rank == 0:
+        S = (M // t) * tp4.N1 * 2
+        peak_hbm = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs", 6650.0) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 6650.0
+        rows = {}
+        for R, ms in out.items():
+            hbm = ((t + 1) * S + t * S) / (ms * 1e-3) / 1e9
+            link = (t - 1) * S / (ms * 1e-3) / 1e9
+            rows[R] = {"ms": round(ms, 4), "hbm_GBs": round(hbm, 1), "hbm_frac_of_measured_peak": round(hbm / peak_hbm, 4),
+                       "nvlink_egress_GBs": round(link, 1), "nvlink_frac_of_770": round(link / 770.0, 4)}
+        print(json.dumps({"workload": f"owner reducer alone (variant {args.red_variant or 'default'}), TP{t}, M={M}, n1=8192, push={'nvls' if args.protocol == 'v3' and t > 1 else 'unicast'}",
+                          "bytes_per_rank": {"hbm_read": (t + 1) * S, "hbm_write": t * S, "nvlink_egress": (t - 1) * S}, "by_R": rows}), flush=True)
+    tp4.barrier()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,13 +260,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="chain", choices=["chain", "boundary"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
     ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
+    ap.add_argument("--red-variant", type=int, default=0, help="boundary / reducer: 1 = warp-per-unit reducer, 3 = TMA-fed reducer, 0 = library default")
     ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")
     args = ap.parse_args()
     if args.m is None:
@@ -225,6 +280,9 @@ def main():
         return
     if args.workload == "boundary":
         run_boundary(args, rank, world, local_rank)
+        return
+    if args.workload == "reducer":
+        run_reducer(args, rank, world, local_rank)
         return
     assert world == max(args.gpus, 1), f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run), got WORLD_SIZE={world}"
     import torch.distributed as dist

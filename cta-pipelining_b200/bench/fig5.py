@@ -53,10 +53,11 @@ def main():
         tp = mt.TensorParallel2(M, X, W1a, W2b)
         r["tp2_cublas_nccl_us"] = measure(tp, a.reps)[0]
         bestc = None
-        for gr in [int(v) for v in a.groups.split(",")]:
+        for gr in [v if v == "ramp" else int(v) for v in a.groups.split(",")]:
             c = mt.Ctapp(M, X, W1a, W2b, a.cfg, a.cfg, gr)
             t = measure(c, a.reps)[0]
             c.pl.check()
+            r[f"ctapp_g{gr}_us"] = t
             if bestc is None or t < bestc[0]:
                 bestc = (t, gr)
         r["ctapp_us"], r["ctapp_group_rows"] = bestc

@@ -14,6 +14,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm2_sm100.cuh"
 #include "reduce_sm100.cuh"
+#include "reduce_tma_sm100.cuh"
 
 using namespace ctapp;
 
@@ -76,7 +77,8 @@ static void* driver_fn(const char* name) {
 }
 
 // bf16 row-major matrix (rows x cols, leading dimension ld elements), box box_cols x box_rows, 128-byte swizzle
-static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows) {
+static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
+                     bool swizzle128 = true) {
   static EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(driver_fn("cuTensorMapEncodeTiled"));
   if (!enc) return fail(-3, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(-1, "matrix base %p is not 16-byte aligned", base);
@@ -86,7 +88,7 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long lon
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %dx%d)", (int)r, rows, cols, ld, box_cols, box_rows);
   return 0;
@@ -257,6 +259,27 @@ static int noalloc_scratch_ptr(int device, unsigned char** out) {
   return 0;
 }
 
+template <int W> static int launch_reduce_tma(const ReduceParams& p, const void* const* inbox, const void* resid, int ppo, int blocks, cudaStream_t s) {
+  using Cfg = RedTmaCfg<W>;
+  ReduceTmaParams tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.r = p;
+  tp.has_resid = resid != nullptr;
+  for (int i = 0; i < W; i++)
+    if (int r = make_tmap(&tp.tmIn[i], inbox[i], static_cast<long long>(ppo) * 128, p.n1, p.n1, Cfg::kChunkCols, kRedUnitRows, false)) return r;
+  if (resid)
+    if (int r = make_tmap(&tp.tmIn[W], resid, p.M, p.n1, p.n1, Cfg::kChunkCols, kRedUnitRows, false)) return r;
+  if (p.x_mc) {
+    CU_OK(cudaFuncSetAttribute(tp_reduce_tma_kernel<W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    tp_reduce_tma_kernel<W, true><<<blocks, kRedThreads, Cfg::kSmemBytes, s>>>(tp);
+  } else {
+    CU_OK(cudaFuncSetAttribute(tp_reduce_tma_kernel<W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    tp_reduce_tma_kernel<W, false><<<blocks, kRedThreads, Cfg::kSmemBytes, s>>>(tp);
+  }
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
@@ -304,6 +327,13 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<1, false>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, false>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<4, false>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<8, false>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<4, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<8, true>));
   if (int r = prepare_kernel<256>()) return r;
   if (int r = prepare_kernel<128>()) return r;
   CU_OK(cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
@@ -468,6 +498,15 @@ int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
   p.limit_ns = limit_ns();
   if (a->M == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a->tma) {   // TMA-fed variant: same protocol, shared-memory staging of the inbox and residual patches
+    ARG(!a->unit_ctr, "the TMA-fed reducer assigns units statically (unit_ctr must be NULL)");
+    switch (a->world) {
+      case 1: return launch_reduce_tma<1>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
+      case 2: return launch_reduce_tma<2>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
+      case 4: return launch_reduce_tma<4>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
+      default: return launch_reduce_tma<8>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
+    }
+  }
   switch (a->world) {
     case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
     case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);

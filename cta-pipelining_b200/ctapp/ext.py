@@ -21,7 +21,7 @@ CSRC = os.path.join(ROOT, "csrc")
 LIB_PATH = os.path.join(ROOT, "libctapp_b200.so")
 BD = BD4 = ROOT   # build directory (the reference kept one per module; here one library serves both)
 SOURCES = ["ctapp_b200.cu"]
-HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
+HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", "reduce_tma_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 STATUS_INTS = 8
@@ -101,7 +101,7 @@ class TpReduceArgs(C.Structure):
                 ("resid", C.c_void_p), ("peer_x", C.c_void_p * MAX_WORLD), ("peer_rowss", C.c_void_p * MAX_WORLD),
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("unit_ctr", C.c_void_p), ("trace", C.c_void_p),
-                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p)]
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("tma", C.c_int)]
 
 
 _SIGS = {
@@ -389,6 +389,7 @@ class Tp4Module:
         a.panels_per_owner, a.tail_cols = int(panels_per_owner), int(tail_cols)
         a.unit_ctr, a.trace, a.status = _ptr(unit_ctr), _ptr(red_trace), _ptr(status)
         a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
+        a.tma = 1 if variant == 3 else 0
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
 

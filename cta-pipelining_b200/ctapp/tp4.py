@@ -103,7 +103,7 @@ class CtappBoundary:
         if protocol in (True, "v3") and not self.nvls:
             log.warning("ctapp: NVLS needs one process per GPU and at least 2 ranks; using unicast pushes")
         assert fusion in ("none", "pdl", "serial"), f"fusion {fusion!r} is not available in this build (none | pdl | serial)"
-        assert red_variant == 1, "only the warp-per-unit reducer (variant 1) exists in this build"
+        assert red_variant in (1, 3), "reducer variants of this build: 1 = warp per unit (register loads), 3 = TMA-fed"
         assert qkv_tile in (256, 128)
         assert down_tail == "auto" or (isinstance(down_tail, int) and 0 <= down_tail <= n1 // 256), down_tail
         self.ext = load_tp4()
@@ -119,7 +119,7 @@ class CtappBoundary:
         self.qkv_sms = self.sms
         self.fusion, self.down_swizzle, self.down_tail, self.steal = fusion, down_swizzle, down_tail, bool(steal)
         self.down_raster = down_raster or 1
-        self.red_threads, self.red_blocks = red_threads, red_blocks or self.R
+        self.red_threads, self.red_blocks, self.red_variant = red_threads, red_blocks or self.R, red_variant
         self.graph_bind = bool(graph_bind)
         self.pdl_trigger = (1 if fusion == "pdl" else 0) if pdl_trigger is None else int(pdl_trigger)
         self.trace = bool(int(os.environ.get("CTAPP_TRACE", "0"))) if trace is None else bool(trace)
@@ -192,7 +192,7 @@ class CtappBoundary:
         self.ext.tp4_reduce(M, self.rank, self.world, 0, self.down_raster, self.red_blocks, self.tile_flags, resid=resid,
                             peer_x=self._peer_x[parity], version=5, epoch_dev=self.epoch_dev, inbox_ptrs=self._inbox_local,
                             peer_rowss=self._peer_rowss[parity], peer_panel_flag=self._peer_pf, rowss_local=self.rowss_local,
-                            panel_done=self.panel_done, panels_per_owner=self.ppo, threads=self.red_threads,
+                            panel_done=self.panel_done, panels_per_owner=self.ppo, threads=self.red_threads, variant=self.red_variant,
                             red_trace=self._tr(self.trace_red), unit_ctr=self.role_ctr[1:] if self.steal else 0,
                             tail_cols=self._tail(M), n1=self.n1, status=self.status, x_mc_ptr=self._x_mc[parity],
                             rowss_mc_ptr=self._rowss_mc[parity], panel_flag_mc_ptr=self._pf_mc)

@@ -151,6 +151,9 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   void* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
+  /* 1 = TMA-fed kernel (loader warp stages 32 x 256 patches of every source in shared memory, 8 adder warps, a publisher
+   * warp; `threads` is ignored, `blocks` CTAs of 320 threads); 0 = warp-per-unit kernel with register loads */
+  int tma;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 

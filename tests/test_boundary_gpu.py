@@ -74,17 +74,17 @@ def _forward_and_check(bds, M, K, n1, N2_, seed, use_resid=True):
         assert int(bd.epoch_dev.item()) == bd.epoch
 
 
-@pytest.mark.parametrize("cta_pair", [True, False])
+@pytest.mark.parametrize("cta_pair,red_variant", [(True, 3), (True, 1), (False, 3), (False, 1)])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
-def test_boundary_one_gpu_plays_all_ranks(world, cta_pair):
+def test_boundary_one_gpu_plays_all_ranks(world, cta_pair, red_variant):
     K, n1, N2_ = 1024 * world if world < 8 else 2048, 512, 256 * world
-    bds = _setup(world, [0] * world, 1024, K, n1, N2_, cta_pair=cta_pair)
+    bds = _setup(world, [0] * world, 1024, K, n1, N2_, cta_pair=cta_pair, red_variant=red_variant)
     for seed, M in enumerate((1024, 256, 640, 128), start=3):   # variable M on one instance, fresh weights per call
         _forward_and_check(bds, M, K, n1, N2_, seed)
 
 
 def test_boundary_no_residual_and_tile128():
-    bds = _setup(2, [0, 0], 512, 512, 768, 512, resid=False, qkv_tile=128, down_tail=0)
+    bds = _setup(2, [0, 0], 512, 512, 768, 512, resid=False, qkv_tile=128, down_tail=0, red_variant=3)
     _forward_and_check(bds, 512, 512, 768, 512, 11, use_resid=False)
     _forward_and_check(bds, 384, 512, 768, 512, 12, use_resid=False)
 
@@ -156,16 +156,16 @@ def test_add_rmsnorm_baseline_kernel():
 
 
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("cta_pair", [True, False])
+@pytest.mark.parametrize("cta_pair,red_variant", [(True, 3), (False, 1), (True, 1)])
 @pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl")])
-def test_boundary_two_gpus_concurrent(world, fusion, cta_pair):
+def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, red_variant):
     """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""
     from ctapp.symm import LocalGroup
     from ctapp.tp4 import CtappBoundary
     K, n1, N2_, max_M = 4096, 8192, 2560, 2048
     grp = LocalGroup(list(range(world)))
     Kr, N2r = K // world, N2_ // world
-    bds = [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", r), protocol="v5", max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair) for r in range(world)]
+    bds = [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", r), protocol="v5", max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, red_variant=red_variant) for r in range(world)]
     Wd, gamma, Wq = ob.make_weights(seed=1, K=K, N2_=N2_, n1=n1)
     sh = [ob.shard_weights(Wd, Wq, gamma, r, world) for r in range(world)]
     wds = [sh[r][0].to(bds[r].dev) for r in range(world)]; wqs = [sh[r][2].to(bds[r].dev) for r in range(world)]

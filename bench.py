@@ -161,7 +161,7 @@ def run_boundary(args, rank, world, local_rank):
     t = world
     Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
     kfull = Kr * t
-    akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4)
+    akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4, down_tail=tp4.N1 // 256)
     g = torch.Generator().manual_seed(0)
     # per-rank shards drawn directly (the full 28672-wide weights never exist in one place; parity is covered by the tests)
     Wd_r = (torch.randn(tp4.N1, Kr, generator=g) * kfull ** -0.5).to(torch.bfloat16).to(dev)
@@ -252,6 +252,78 @@ def run_reducer(args, rank, world, local_rank):
     tp4.barrier()
 
 
+def run_stages(args, rank, world, local_rank):
+    """Stage breakdown of the boundary (what reference bench/v5_stages.py:40-277 reports): the producer GEMM storing locally
+    (mode 0) and scattering to the owners with flags (mode 7), the owner reducer alone, the consumer GEMM plain (mode 0) and
+    waiting per panel on flags that are already up (mode 5), and the whole boundary; back-to-back mean ms, max over ranks.  The
+    scatter's NVLink egress is (t - 1) / t of the producer's output."""
+    import torch.distributed as dist
+    from ctapp import tp4
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29580")
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    tp4.GLOO = dist.new_group(backend="gloo")
+    M, t = args.m, world
+    Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
+    akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4, down_tail=tp4.N1 // 256)
+    g = torch.Generator().manual_seed(0)
+    Wd = (torch.randn(tp4.N1, Kr, generator=g) * (Kr * t) ** -0.5).to(torch.bfloat16).to(dev)
+    Wq = (torch.randn(N2r, tp4.N1, generator=g) * tp4.N1 ** -0.5).to(torch.bfloat16).to(dev)
+    h = torch.randn(M, Kr, generator=g).to(torch.bfloat16).to(dev)
+    resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
+    ext, iters = bd.ext, max(args.steps, 10)
+    y0 = torch.empty(M, tp4.N1, dtype=torch.bfloat16, device=dev)
+
+    def b2b(fn, prep=None):
+        for _ in range(3):
+            if prep:
+                prep()
+            fn()
+        torch.cuda.synchronize(dev); tp4.barrier()
+        ts = []
+        for _ in range(iters):          # each call bracketed: stages that wait for peers must start together
+            if prep:
+                prep()
+            torch.cuda.synchronize(dev); tp4.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize(dev)
+            ts.append(a.elapsed_time(b))
+        v = torch.tensor([statistics.median(ts)], dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX, group=tp4.GLOO)
+        return float(v.item())
+
+    def step():
+        bd.epoch += 1
+        ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, M, bd.role_ctr)
+
+    res = {}
+    res["producer_mode0_local"] = b2b(lambda: ext.tp4_down(h, Wd, y0, 1, 1, 0, rank, t, 0, sms=bd.sms, tail_cols=bd._tail(M), cta_pair=bd.cta_pair))
+    res["producer_mode7_scatter"] = b2b(lambda: bd._down_v5(h, Wd, M), step)
+    res["reducer_alone"] = b2b(lambda: bd._reduce_v5(M, resid, bd.epoch & 1))            # flags of the last scatter are still up
+    res["consumer_mode0"] = b2b(lambda: ext.tp4_qkv(bd.xbufs[bd.epoch & 1][:M], Wq, bd._out_full[:M], bd.qkv_raster, bd.qkv_swizzle, 0, 0, sms=bd.qkv_sms,
+                                                   tile=bd.qkv_tile, cta_pair=bd.cta_pair))
+    res["consumer_mode5_flags_up"] = b2b(lambda: bd._qkv_v5(Wq, M, bd.epoch & 1))
+    res["boundary"] = b2b(lambda: bd.forward(h, resid, Wd, Wq))
+    bd.check()
+    if rank == 0:
+        out_bytes = M * tp4.N1 * 2
+        egress = (t - 1) / t * out_bytes
+        extra = max(res["producer_mode7_scatter"] - res["producer_mode0_local"], 1e-9)
+        print(json.dumps({"workload": f"TP{t} boundary {args.shape} stage breakdown, M={M}, R={bd.R}, push={'nvls' if bd.nvls else 'unicast'}",
+                          "ms": {k: round(v, 4) for k, v in res.items()},
+                          "scatter": {"nvlink_egress_bytes": int(egress), "egress_GBs_over_kernel": round(egress / (res["producer_mode7_scatter"] * 1e-3) / 1e9, 1),
+                                      "penalty_vs_local_store": round(res["producer_mode7_scatter"] / res["producer_mode0_local"], 4),
+                                      "extra_ms": round(extra, 4)}}), flush=True)
+    tp4.barrier()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -260,7 +332,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
@@ -283,6 +355,9 @@ def main():
         return
     if args.workload == "reducer":
         run_reducer(args, rank, world, local_rank)
+        return
+    if args.workload == "stages":
+        run_stages(args, rank, world, local_rank)
         return
     assert world == max(args.gpus, 1), f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run), got WORLD_SIZE={world}"
     import torch.distributed as dist

@@ -94,7 +94,8 @@ class Model:
         self.ones = torch.ones(HIDDEN, dtype=torch.bfloat16, device=dev)
         self.ext = tp4.load_tp4()
         L0 = self.layers[0]
-        self.ba = tp4.CtappBoundary(max_M, L0.o.shape[1], L0.gate_up.shape[0], rank, t, None, dev, protocol="v5", max_M=max_M, fusion=fusion, qkv_raster=3, qkv_swizzle=4)
+        self.ba = tp4.CtappBoundary(max_M, L0.o.shape[1], L0.gate_up.shape[0], rank, t, None, dev, protocol="v5", max_M=max_M, fusion=fusion, qkv_raster=3, qkv_swizzle=4,
+                                    down_tail=HIDDEN // 256)     # short producer (K = 8192 / t): panel-major, so panels complete one by one
         self.bb = tp4.CtappBoundary(max_M, L0.down.shape[1], L0.qkv.shape[0], rank, t, None, dev, protocol="v5", max_M=max_M, fusion=fusion)
         self.y = torch.empty(max_M, HIDDEN, dtype=torch.bfloat16, device=dev)
         self.xn = torch.empty(max_M, HIDDEN, dtype=torch.bfloat16, device=dev)

@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
       int stage = 0; uint32_t phase = 0; int sq = 0; uint32_t sphase = 0;
       int k_static = 0, ntiles_done = 0;
       uint32_t armed = 0, armed_parity = 0;
+      uint32_t panel_seen[4] = {0, 0, 0, 0};
       auto pop = [&]() -> int {
         if (p.mode == kModeChain) { const int idx = atomicAdd(p.src.head, 1); return idx < p.num_tiles ? idx : -1; }
         const int idx = pair + (k_static++) * npairs;
@@ -138,12 +139,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         const int m = 2 * mp + static_cast<int>(crank);   // this CTA's 128-row panel
         if (p.stamps && ntiles_done == 0) p.stamps[blockIdx.x * 8 + 1] = globaltimer();
         if (p.mode == kModeChain && !p.skip_wait) fence_proxy_async_global();   // peer-written A rows vs the TMA loads below
-        if (p.mode == kModeTpConsumer && p.panel_flag && m < p.panels) {
+        if (p.mode == kModeTpConsumer && p.panel_flag && m < p.panels && !(m < 128 && (panel_seen[m >> 5] >> (m & 31) & 1u))) {
           int seen;
           if (!spin_acquire_sys(p.panel_flag + m, PredGe{epoch}, limit, seen)) {
             report_status(p.status, kStatusTimeoutPanel, m, epoch, seen); abort_pair(kStatusTimeoutPanel); break;
           }
           fence_proxy_async_global();
+          if (m < 128) panel_seen[m >> 5] |= 1u << (m & 31);   // a panel flag never goes back within a launch: ask once
         }
         const uint32_t full0 = mapa_u32(full, 0);   // the leader's full[0] as a cluster address; stages are 8 bytes apart
         next = -2;
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
     uint8_t* stage_buf = sD + ew * (2 * kStageRows * kStoreCols * 2);
     int sq = 0; uint32_t sphase = 0; uint32_t it = 0; uint32_t cbuf = 0; uint32_t epi_phase = 0, published = 0;
     bool ready_checked = p.dst_ready == nullptr;
+    uint32_t epi_seen[4] = {0, 0, 0, 0};
     auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
       const bool ok = mbar_wait_cluster(bar, parity, s_abort, limit);
       return __all_sync(0xffffffffu, ok);
@@ -244,7 +247,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
 
       float scale = 1.0f;
       if (p.mode == kModeTpConsumer && p.rowss && valid) {
-        if (lane == 0 && p.panel_flag) (void)ld_acquire_sys(p.panel_flag + m);
+        if (p.panel_flag && !(m < 128 && (epi_seen[m >> 5] >> (m & 31) & 1u))) {   // rowss was pushed before the flag: acquire once per panel
+          if (lane == 0) (void)ld_acquire_sys(p.panel_flag + m);
+          if (m < 128) epi_seen[m >> 5] |= 1u << (m & 31);
+        }
         __syncwarp();
         const int row = m * BM + row_in_tile;
         if (row < p.M) scale = rsqrtf(__ldcg(p.rowss + row) * p.inv_k + p.eps);

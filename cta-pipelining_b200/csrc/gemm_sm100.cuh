@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       int stage = 0; uint32_t phase = 0; int sq = 0; uint32_t sphase = 0;
       uint32_t armed = 0, armed_parity = 0;   // per stage: has a load been issued, and in which phase
       int k_static = 0, ntiles_done = 0;
+      uint32_t panel_seen[4] = {0, 0, 0, 0};
       auto pop = [&]() -> int {
         if (p.mode == kModeChain) { const int idx = atomicAdd(p.src.head, 1); return idx < p.num_tiles ? idx : -1; }
         const int idx = static_cast<int>(blockIdx.x) + (k_static++) * static_cast<int>(gridDim.x);
@@ -178,12 +179,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         int m, n;
         if (p.mode == kModeChain) { m = tile / p.tiles_n; n = tile - m * p.tiles_n; } else decode_tile(p, tile, m, n);
         if (p.stamps && ntiles_done == 0) { p.stamps[blockIdx.x * 8 + 1] = globaltimer(); }
-        if (p.mode == kModeTpConsumer && p.panel_flag) {
+        if (p.mode == kModeTpConsumer && p.panel_flag && !(m < 128 && (panel_seen[m >> 5] >> (m & 31) & 1u))) {
           int seen;
           if (!spin_acquire_sys(p.panel_flag + m, PredGe{epoch}, limit, seen)) {
             report_status(p.status, kStatusTimeoutPanel, m, epoch, seen); *s_abort = kStatusTimeoutPanel; break;
           }
           fence_proxy_async_global();
+          if (m < 128) panel_seen[m >> 5] |= 1u << (m & 31);   // a panel flag never goes back within a launch: ask once
         }
         next = -2;
         for (int kb = 0; kb < KB; kb++) {
@@ -256,6 +258,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     uint8_t* stage_buf = sD + ew * (2 * kStageRows * kStoreCols * 2);
     int sq = 0; uint32_t sphase = 0; uint32_t it = 0; uint32_t cbuf = 0; uint32_t epi_phase = 0;
     bool ready_checked = p.dst_ready == nullptr;
+    uint32_t epi_seen[4] = {0, 0, 0, 0};
     // every lane polls (each needs its own acquire); the outcome is made warp-uniform so the warp never splits
     auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
       const bool ok = mbar_wait(bar, parity, s_abort, limit);
@@ -277,7 +280,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
       float scale = 1.0f;
       if (p.mode == kModeTpConsumer && p.rowss) {
-        if (lane == 0 && p.panel_flag) (void)ld_acquire_sys(p.panel_flag + m);   // rowss was pushed before the flag
+        if (p.panel_flag && !(m < 128 && (epi_seen[m >> 5] >> (m & 31) & 1u))) {   // rowss was pushed before the flag: acquire once per panel
+          if (lane == 0) (void)ld_acquire_sys(p.panel_flag + m);
+          if (m < 128) epi_seen[m >> 5] |= 1u << (m & 31);
+        }
         __syncwarp();
         const int row = m * BM + row_in_tile;
         if (row < p.M) scale = rsqrtf(__ldcg(p.rowss + row) * p.inv_k + p.eps);

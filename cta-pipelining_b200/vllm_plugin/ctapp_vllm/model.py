@@ -87,7 +87,7 @@ class CtappLlamaModel(LlamaModel):
         self._pool_b = CtappBoundaryPool(l0.mlp.down_proj.weight.shape[1], l0.self_attn.qkv_proj.weight.shape[0], rank, t, group, device,
                                          qkv_raster=2, qkv_swizzle=1, qkv_tile=k["qkv_tile"], **common)
         self._pool_a = CtappBoundaryPool(l0.self_attn.o_proj.weight.shape[1], l0.mlp.gate_up_proj.weight.shape[0], rank, t, group, device,
-                                         qkv_raster=3, qkv_swizzle=4, qkv_tile=256, **common)
+                                         qkv_raster=3, qkv_swizzle=4, qkv_tile=256, down_tail=hidden // 256, **common)
         logger.warning("ctapp_vllm rank %d: set-up done (%s)", rank, {kk: v for kk, v in k.items() if kk != "enabled"})
 
     def _boundaries(self, M):

@@ -52,13 +52,17 @@ def nvls_probes(rank, world, dev, gn):
     exp = sum(d.float() for d in datas).to(torch.bfloat16)
     d_ulp = (out.cpu().view(torch.int16).int() - exp.view(torch.int16).int()).abs()
     if int(d_ulp.max()) > 1:
-        fails.append(f"mm_ld_reduce_bf16: off by {int(d_ulp.max())} ulp")
+        fails.append(f"mm_ld_reduce_bf16: off by {int(d_ulp.max())} ulp ({int((d_ulp > 1).sum())} of {n} beyond one)")
     if world >= 3:      # 256 + 1 + 1 (+...) only survives when the switch accumulates in fp32
         vals = [256.0] + [1.0] * (world - 1)
         lb.fill_(vals[rank]); _sync(dev)
         ext.mm_ld_reduce_bf16(lh.multicast_ptr, out); _sync(dev)
-        if not bool((out.cpu() == torch.tensor(sum(vals)).to(torch.bfloat16)).all()):
-            fails.append("mm_ld_reduce_bf16 does not accumulate in fp32")
+        # sequential bf16 accumulation would stay at 256 (256 + 1 rounds back to 256); an fp32 accumulator holds 256 + (world - 1)
+        # and only the final conversion decides between the two neighbouring bf16 values
+        got = out.cpu().float()
+        exact = float(sum(vals))
+        if not (bool((got > 256.0).all()) and bool(((got - exact).abs() <= 2.0).all())):
+            fails.append(f"mm_ld_reduce_bf16 does not accumulate in fp32: got {got[0].item()} for {exact}")
     slots, iters = 64, 500
     db, dh = symm_empty((slots * 32 * 8,), torch.bfloat16, dev, gn, rank, multicast=True)
     fl, fh2 = symm_empty((slots,), torch.int32, dev, gn, rank, multicast=True)

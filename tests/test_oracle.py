@@ -110,6 +110,19 @@ def test_unit_map_follows_producer_order():
             assert all(units[4 * i + q] == (units[4 * i][0], units[4 * i][1], q) for i in range(len(units) // 4) for q in range(4))
 
 
+def test_unit_map_for_panel_major_and_plain_m_fast_orders():
+    # tail == all n-tiles: the producer walks panel by panel (short producers); tail == 0: m fastest everywhere
+    for M, world, C in [(1024, 4, 32), (1024, 2, 0), (640, 4, 32), (2048, 8, 0)]:
+        TM, TN = M // 128, 32
+        prod = [ob.remap_tile(L, TM, TN, C) for L in range(TM * TN)]
+        if C == TN:
+            assert prod[:TN] == [(0, n) for n in range(TN)]
+        for rank in range(world):
+            Pr = ob.panels_owned(M, rank, world)
+            units = [ob.unit_map(u, Pr, TN, C) for u in range(Pr * TN * 4)]
+            assert [(j * world + rank, n) for (j, n, q) in units if q == 0] == [(m, n) for (m, n) in prod if m % world == rank]
+
+
 def test_tail_and_ppo_rules():
     assert ob.tail_cols(4096) == 16 and ob.tail_cols(2048) == 16 and ob.tail_cols(1920) == 8 and ob.tail_cols(128) == 8
     assert ob.tail_cols(4096, raster=2) == 0 and ob.tail_cols(4096, swizzle=2) == 0

@@ -136,9 +136,10 @@ class Chain:
     tiles land in the memory of ``devices[g+1]`` and are announced in that GPU's work queue.  Repeated devices are
     allowed (stages then run back to back on that GPU's stream)."""
 
-    def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0):
+    def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0, stamps=False):
         self.ext = load()
         self.sms = sms
+        self.stamps = None       # per stage: 8 int64 per CTA (ctapp.timeline reads them), when ``stamps`` is set
         self.M, self.K, self.widths, self.fence, self.skip_wait = M, K, list(widths), fence, skip_wait
         self.cfg = list(cfg) if isinstance(cfg, (list, tuple)) else [cfg] * len(self.widths)
         self.devs = [torch.device("cuda", d) for d in devices]
@@ -166,6 +167,8 @@ class Chain:
                 self.tail.append(torch.zeros(1, device=dev, **i32))
             self.head.append(torch.zeros(1, device=dev, **i32))
             self.status.append(new_status(dev))
+            if stamps:
+                self.stamps = (self.stamps or []) + [torch.zeros(256 * 8, dtype=torch.int64, device=dev)]
             out_dev = self.devs[g + 1] if g + 1 < L else dev
             self.Y.append(torch.empty(M, self.widths[g], device=out_dev, dtype=torch.bfloat16))
             if g + 1 < L:
@@ -199,7 +202,8 @@ class Chain:
                                     self.dep_off[g], self.dep_cons[g], self.sb[g],
                                     None if last else self.entries[g + 1], None if last else self.head[g + 1],
                                     None if last else self.tail[g + 1], self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
-                                    tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms)
+                                    tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms,
+                                    stamps=self.stamps[g] if self.stamps else None)
         return self.Y[-1]
 
     def run(self, X, Ws):

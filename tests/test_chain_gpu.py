@@ -190,3 +190,29 @@ def test_gated_harness_and_methods_two_gpus():
     slow = SlowHost(M, X, W1.to(mt.dev(0)), W2.to(mt.dev(1)), 10, 10, 2)
     t_slow = measure(slow, reps=5, warmup=2)[0]
     assert t_slow < 3 * t_fast + 200, (t_fast, t_slow)     # microseconds: the 10 ms host sleep is outside the window
+
+
+@pytest.mark.multigpu(2)
+def test_clock_offset_and_chain_timeline_two_gpus():
+    """The bounded flag ping-pong between two GPUs gives a stable clock offset and a round trip of a few microseconds, and the
+    per-CTA stamps of a pipelined run, put on one clock, tell the pipelining story: the consumer is resident from the start, gets
+    its first tile only after the producer has published, and finishes after the producer."""
+    from ctapp.pipeline import Chain
+    from ctapp.timeline import chain_timeline, clock_offset
+    off1, rtt1 = clock_offset(0, 1)
+    off2, rtt2 = clock_offset(0, 1)
+    assert 500 < rtt1 < 50000 and 500 < rtt2 < 50000, (rtt1, rtt2)       # ns
+    assert abs(off1 - off2) < 5000, (off1, off2)
+    M, K, N = 4096, 8192, 8192
+    ch = Chain(M, K, [N, N], [0, 1], cfg=10, group_rows=2, stamps=True)
+    X, Ws = oc.make_chain_inputs(M, K, [N, N], seed=0)
+    Xa, Wd = X.cuda(0), [Ws[0].cuda(0), Ws[1].cuda(1)]
+    for _ in range(2):
+        ch.run(Xa, Wd)
+        ch.check()
+    tl = chain_timeline(ch)
+    p, c = tl
+    assert p["ctas"] == 148 and c["ctas"] == 148 and p["tiles"] == 16 * 32 and c["tiles"] == 16 * 32
+    assert c["first_tile_min_us"] > p["first_tile_min_us"] + 5, (p, c)     # nothing to consume before the first panel is published
+    assert c["exit_max_us"] > p["exit_max_us"], (p, c)
+    assert c["first_tile_min_us"] < p["exit_max_us"], "the consumer started only after the producer had finished: no pipelining"

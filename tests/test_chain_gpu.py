@@ -212,7 +212,8 @@ def test_clock_offset_and_chain_timeline_two_gpus():
         ch.check()
     tl = chain_timeline(ch)
     p, c = tl
-    assert p["ctas"] == 148 and c["ctas"] == 148 and p["tiles"] == 16 * 32 and c["tiles"] == 16 * 32
+    # 16 pair-rows x 32 n-tiles; both CTAs of a pair count the pair's tiles
+    assert p["ctas"] == 148 and c["ctas"] == 148 and p["tiles"] == 2 * 16 * 32 and c["tiles"] == 2 * 16 * 32
     assert c["first_tile_min_us"] > p["first_tile_min_us"] + 5, (p, c)     # nothing to consume before the first panel is published
     assert c["exit_max_us"] > p["exit_max_us"], (p, c)
     assert c["first_tile_min_us"] < p["exit_max_us"], "the consumer started only after the producer had finished: no pipelining"

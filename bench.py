@@ -182,6 +182,19 @@ def run_boundary(args, rank, world, local_rank):
     res["cublas_nccl_fusednorm"] = tp4.time_step(lambda: st.forward(h_r, resid), dev, iters, warm)
     st2 = tp4.NcclBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
     res["cublas_nccl_eagernorm"] = tp4.time_step(lambda: st2.forward(h_r, resid), dev, iters, warm)
+    unavailable = {}
+    if args.baselines == "strong" and t > 1:
+        for name, cls in (("cublas_multimem_ar_eagernorm", tp4.MultimemBoundary), ("asynctp_matmul_reduce_scatter", tp4.AsyncTpBoundary)):
+            try:
+                bs = cls(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
+                res[name] = tp4.time_step(lambda: bs.forward(h_r, resid), dev, iters, warm)
+            except Exception as e:  # noqa: BLE001  (a baseline that this torch build cannot run is reported, not fatal)
+                unavailable[name] = repr(e)[:200]
+            ok_all = torch.tensor([0 if name in unavailable else 1])
+            dist.all_reduce(ok_all, op=dist.ReduceOp.MIN, group=tp4.GLOO)
+            if not int(ok_all.item()):
+                res.pop(name, None)
+                unavailable.setdefault(name, "failed on another rank")
     # agreement of the two paths on this rank's output shard (bf16 tolerance; different rounding points)
     o1 = bd.forward(h_r, resid).float(); o2 = st.forward(h_r, resid).float()
     torch.cuda.synchronize(dev)
@@ -195,7 +208,7 @@ def run_boundary(args, rank, world, local_rank):
                           "n_gpus": t, "fusion": args.fusion, "R": bd.R, "push": "nvls multimem" if bd.nvls else "unicast", "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
                           "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
                           "tflops_per_gpu_b2b": flops / (b2b * 1e-3) / 1e12, "frac_of_burst_peak": flops / (b2b * 1e-3) / 1e12 / burst,
-                          "out_rel_vs_stock": rel, "iters": iters}), flush=True)
+                          "out_rel_vs_stock": rel, "iters": iters, "unavailable": unavailable}), flush=True)
 
 
 def run_reducer(args, rank, world, local_rank):
@@ -338,6 +351,8 @@ def main():
                     "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
     ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
+    ap.add_argument("--baselines", default="stock", choices=["stock", "strong"],
+                    help="boundary: strong = also torch's multimem all-reduce and async-TP (fused matmul + reduce-scatter) boundaries")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
     ap.add_argument("--red-variant", type=int, default=0, help="boundary / reducer: 1 = warp-per-unit reducer, 3 = TMA-fed reducer, 0 = library default")
     ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")

@@ -450,6 +450,83 @@ class NcclFusedNormBoundary(_Base):
         return torch.mm(self.xn[:M], self.Wq.t(), out=self.out[:M])
 
 
+class MultimemBoundary(_Base):
+    """cuBLAS GEMM into a symmetric buffer + torch's in-switch (multimem) all-reduce + eager add and norm (reference
+    ctapp/tp4.py:573-583).  Needs torch symmetric memory with multicast support."""
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import torch.distributed._symmetric_memory as symm_mem
+        self.y = symm_mem.empty(self.M, self.Wd.shape[0], dtype=DTYPE, device=self.dev)
+        self._h = symm_mem.rendezvous(self.y, self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name)
+
+    def forward(self, h_r, resid=None):
+        torch.mm(h_r, self.Wd.t(), out=self.y)
+        torch.ops.symm_mem.multimem_all_reduce_(self.y, "sum", self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name)
+        return self._post(self.y, resid)
+
+
+class AsyncTpBoundary(_Base):
+    """torch's fused matmul + reduce-scatter (the async-TP decomposition), norm on the own rows, all-gather, GEMM (reference
+    ctapp/tp4.py:621-638)."""
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import torch.distributed._symmetric_memory as symm_mem
+        self._gname = self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name
+        symm_mem.enable_symm_mem_for_group(self._gname)
+        self.full = torch.empty(self.M, self.Wd.shape[0], dtype=DTYPE, device=self.dev)
+
+    def forward(self, h_r, resid=None):
+        from torch.distributed._symmetric_memory import _fused_matmul_reduce_scatter
+        m = self.M // self.world
+        ys = _fused_matmul_reduce_scatter(h_r, self.Wd.t(), "sum", 0, self._gname)
+        if resid is not None:
+            ys = ys + resid[self.rank * m:(self.rank + 1) * m]
+        self._x = ys                                             # own rows only
+        dist.all_gather_into_tensor(self.full, rmsnorm_gamma(ys, self.gamma))
+        return torch.mm(self.full, self.Wq.t())
+
+
+class FlashInferBoundary(_Base):
+    """cuBLAS GEMM + FlashInfer's fused all-reduce + residual + RMSNorm kernel (the serving stacks' production path) + cuBLAS
+    GEMM (reference ctapp/tp4.py:586-618).  The reduction is not overlapped with the GEMM.  FlashInfer builds its kernels on
+    first use."""
+
+    def __init__(self, *a, use_oneshot=None):
+        super().__init__(*a)
+        from flashinfer.comm import trtllm_create_ipc_workspace_for_all_reduce_fusion as create
+        n1 = self.Wd.shape[0]
+        self.use_oneshot = use_oneshot
+        self.ipc, self.ws = create(self.rank, self.world, self.M, n1, group=dist.group.WORLD)[:2]
+        self.y = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
+        self.resid_out = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
+        self.norm_out = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
+        self.zeros = None
+        self.gamma_c = self.gamma.contiguous()
+
+    def forward(self, h_r, resid=None):
+        from flashinfer.comm import AllReduceFusionPattern, trtllm_allreduce_fusion
+        if resid is None:
+            if self.zeros is None:
+                self.zeros = torch.zeros_like(self.y)
+            resid = self.zeros
+        torch.mm(h_r, self.Wd.t(), out=self.y)
+        trtllm_allreduce_fusion(allreduce_in=self.y, world_size=self.world, world_rank=self.rank, token_num=self.M, hidden_dim=self.y.shape[1],
+                                workspace_ptrs=self.ws, launch_with_pdl=False, trigger_completion_at_end=True, fp32_acc=True,
+                                pattern_code=AllReduceFusionPattern.kARResidualRMSNorm, use_oneshot=self.use_oneshot, allreduce_out=None,
+                                residual_in=resid, residual_out=self.resid_out, norm_out=self.norm_out, quant_out=None, scale_out=None,
+                                rms_gamma=self.gamma_c, rms_eps=EPS, scale_factor=None, layout_code=None)
+        self._x = self.resid_out
+        return torch.mm(self.norm_out, self.Wq.t())
+
+    def destroy(self):
+        from flashinfer.comm import trtllm_destroy_ipc_workspace_for_all_reduce_fusion as destroy
+        torch.cuda.synchronize(self.dev)
+        dist.barrier()
+        destroy(self.ipc)
+
+
 # --------------------------------------------------------------------------- references
 @torch.no_grad()
 def one_gpu_reference(h_full, Wdown_full, resid, gamma, Wqkv_full, eps=EPS):

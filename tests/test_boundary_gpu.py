@@ -182,3 +182,26 @@ def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, red_variant):
         assert _ulp_frac(out, out_model) >= 0.98
         mx, mean = oc.error_stats(out, out_model)
         assert mx <= 2e-2 and mean <= 1e-3
+
+
+def test_boundary_pool_one_instance_serves_every_supported_M():
+    """``CtappBoundaryPool`` (reference tests/test_tp4_pool.py:17-83): unsupported token counts give None (the caller keeps its
+    stock path), every supported one is served by the same instance with the weights of the call."""
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundaryPool
+    K, n1, N2_ = 512, 512, 512
+    pool = CtappBoundaryPool(K, N2_, 0, 1, LocalGroup([0]), torch.device("cuda", 0), min_M=256, max_M=1024, n1=n1, fusion="serial")
+    assert pool.get(200) is None and pool.get(128) is None and pool.get(2048) is None and pool.get(1000) is None
+    seen = set()
+    for i, M in enumerate((512, 1024, 256, 768, 512)):
+        bd = pool.get(M)
+        seen.add(id(bd))
+        Wd, gamma, Wq = ob.make_weights(seed=60 + i, K=K, N2_=N2_, n1=n1)
+        h, resid = ob.make_inputs(M, seed=70 + i, K=K, n1=n1)
+        wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, 0, 1)
+        out = bd.forward(h.cuda(), resid.cuda(), wd.cuda(), wqf.cuda())
+        bd.check()
+        x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, 1)
+        assert out.shape == (M, N2_) and bd.x().shape == (M, n1)
+        assert _ulp_frac(bd.x().cpu(), x_model) >= 0.99 and _ulp_frac(out.cpu(), out_model) >= 0.98, (i, M)
+    assert len(seen) == 1 and len(pool._inst) == 1

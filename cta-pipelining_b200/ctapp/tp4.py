@@ -18,10 +18,6 @@ from __future__ import annotations
 
 import logging
 import os
-import statistics
-import sys
-import time
-import traceback
 
 import torch
 import torch.distributed as dist

@@ -1,6 +1,4 @@
 """The multi-rank host logic on the CPU: world_size-2 process groups over gloo (no GPU)."""
-import pytest
-
 from oracle import boundary as ob
 from oracle import chain as oc
 

@@ -138,7 +138,11 @@ def workload_config(args, n):
     return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
                         + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
             "M": args.m, "N": NK, "K": NK, "stages": n, "tile": "256x256x64 per CTA pair (cta_group::2)", "parallelism": f"pp{n}",
-            "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)"}
+            "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)",
+            "steps_overlap": "none (one GEMM per step)" if n == 1 else
+            "consecutive steps stream through the stages like batches through a layer pipeline: every link (buffer, queue, "
+            "ready flag) is doubled, so a stage starts step e+1 while its successor still consumes step e; at most two steps "
+            "in flight per link; ms_per_step is the K steps' total time / K, fill included"}
 
 
 def run_boundary(args, rank, world, local_rank):
@@ -348,7 +352,8 @@ def main():
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
-                    "and last, large in the middle) or 'auto' (8 for one stage, 2 otherwise: measured best on 2 GPUs)")
+                    "and last, large in the middle) or 'auto' (8: every stage then walks 8 tile rows per weight tile; consecutive steps overlap, so "
+                    "the longer fill of a large group is paid once per run, not per step)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
     ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
     ap.add_argument("--baselines", default="stock", choices=["stock", "strong"],
@@ -414,7 +419,7 @@ def main():
     Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
 
     gr = args.group_rows
-    gr = (8 if world == 1 else 2) if gr == "auto" else (gr if gr == "ramp" else int(gr))
+    gr = 8 if gr == "auto" else (gr if gr == "ramp" else int(gr))
     args.group_rows = gr
     if world == 1:
         chain = Chain(M, NK, [NK], [local_rank], cfg=GEMM_CFG, group_rows=args.group_rows)

@@ -380,6 +380,8 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   p.dep_offsets = a->dep_offsets; p.dep_consumers = a->dep_consumers; p.scoreboard = a->scoreboard;
   p.dst = Queue{a->dst.entries, a->dst.head, a->dst.tail, a->dst.cap};
   p.tiles_n2 = a->tiles_n2; p.rowpanel = a->rowpanel; p.skip_wait = a->skip_wait;
+  ARG(a->src_group >= 0 && a->src_group <= 1024, "bad src_group %d", a->src_group);
+  p.src_group = a->src_group;
   p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
   p.status = a->status; p.stamps = a->stamps;
   if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream));

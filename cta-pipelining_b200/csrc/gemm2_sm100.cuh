@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           if (tile >= 0 && p.status && ld_relaxed_gpu(p.status) != 0) tile = -1;
           if (tile >= 0 && p.mode == kModeChain && !p.skip_wait) {
             int seen;
-            const int slot = tile % p.src.cap;
+            const int slot = queue_slot(p, tile);
             if (!spin_acquire_sys(p.src.entries + slot, PredNe{-1}, limit, seen)) {
               report_status(p.status, kStatusTimeoutQueue, slot, 0, seen); abort_pair(kStatusTimeoutQueue); break;
             }

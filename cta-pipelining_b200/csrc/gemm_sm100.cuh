@@ -49,7 +49,7 @@ struct alignas(64) GemmParams {
   const int* dep_consumers;
   int* scoreboard;
   Queue dst;
-  int tiles_n2, rowpanel, skip_wait;
+  int tiles_n2, rowpanel, skip_wait, src_group;
   const int* dst_ready;
   int ready_value;
   // tensor-parallel boundary
@@ -78,6 +78,18 @@ template <int BN> struct GemmCfg {
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;   // + alignment slack
   static constexpr uint32_t kTmemCols = 2 * BN;
 };
+
+// Chain mode: which slot of the source queue the idx-th pop reads.  The producer publishes a finished row panel as tiles_n
+// consecutive slots.  With src_group = g > 1 the pops walk windows of g such panels n-tile major (slot 0 of every panel of the
+// window, then slot 1, ...), so that g row panels share each weight tile while it is hot in L2; the last window takes the
+// panels that are left.  A permutation of the slots: every slot is still read exactly once.
+__device__ __forceinline__ int queue_slot(const GemmParams& p, int idx) {
+  const int tn = p.tiles_n, g = p.src_group;
+  if (g <= 1) return idx % p.src.cap;
+  const int wsz = g * tn, base = (idx / wsz) * wsz, left = (p.src.cap - base) / tn;
+  const int gw = left < g ? left : g, r = idx - base;
+  return base + (r % gw) * tn + r / gw;
+}
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int L, int& m, int& n) {
   const int TM = p.tiles_m, TN = p.tiles_n;
@@ -161,7 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (tile >= 0 && p.status && ld_relaxed_gpu(p.status) != 0) tile = -1;   // another CTA gave up: stop taking work
         if (tile >= 0 && p.mode == kModeChain && !p.skip_wait) {
           int seen;
-          const int slot = tile % p.src.cap;
+          const int slot = queue_slot(p, tile);
           if (!spin_acquire_sys(p.src.entries + slot, PredNe{-1}, limit, seen)) {
             report_status(p.status, kStatusTimeoutQueue, slot, 0, seen); *s_abort = kStatusTimeoutQueue; break;
           }

@@ -96,6 +96,27 @@ def _tile(ext, cfg):
     return int(s[0]), int(s[1])
 
 
+def pop_slots(ntiles, tn, group):
+    """Queue slot read by the i-th pop of a consuming stage (host model of the kernel's ``queue_slot``): windows of ``group``
+    published row panels, n-tile major inside a window; the last window takes the panels that are left.  group <= 1: queue order."""
+    idx = torch.arange(ntiles)
+    if group <= 1:
+        return idx.int()
+    wsz = group * tn
+    base = (idx // wsz) * wsz
+    gw = torch.clamp((ntiles - base) // tn, max=group)
+    r = idx - base
+    return (base + (r % gw) * tn + r // gw).int()
+
+
+def consumer_window(group_rows, rowpanel, bm_prev, bm):
+    """Window (in this stage's row panels) a consuming stage pops in: the rows its producer finishes together."""
+    if not rowpanel or not isinstance(group_rows, int) or group_rows <= 0:
+        return 0
+    g = group_rows * bm_prev // bm
+    return g if g > 1 else 0
+
+
 class Pipeline:
     """2-layer CTA-pipelined run: the producer GEMM on devA stores Y1 into devB's memory tile by tile, the consumer GEMM
     on devB starts each tile as soon as the row panel it reads is complete.  Same constructor, attributes and methods
@@ -136,7 +157,8 @@ class Chain:
     tiles land in the memory of ``devices[g+1]`` and are announced in that GPU's work queue.  Repeated devices are
     allowed (stages then run back to back on that GPU's stream)."""
 
-    def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0, stamps=False):
+    def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0, stamps=False,
+                 consumer_group="auto"):
         self.ext = load()
         self.sms = sms
         self.stamps = None       # per stage: 8 int64 per CTA (ctapp.timeline reads them), when ``stamps`` is set
@@ -153,6 +175,8 @@ class Chain:
         tiles = [_tile(self.ext, c) for c in self.cfg]
         i32 = dict(dtype=torch.int32)
         L = len(self.widths)
+        self.src_group = [0] + [consumer_window(group_rows, self.rowpanel, tiles[g - 1][0], tiles[g][0]) if consumer_group == "auto"
+                                else int(consumer_group) for g in range(1, L)]
         self.tn = [-(-n // t[1]) for n, t in zip(self.widths, tiles)]
         self.ntiles = [-(-M // t[0]) * tn for t, tn in zip(tiles, self.tn)]
         self.entries, self.head, self.tail, self.Y, self.status = [], [], [], [], []
@@ -203,7 +227,7 @@ class Chain:
                                     None if last else self.entries[g + 1], None if last else self.head[g + 1],
                                     None if last else self.tail[g + 1], self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
                                     tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms,
-                                    stamps=self.stamps[g] if self.stamps else None)
+                                    stamps=self.stamps[g] if self.stamps else None, src_group=self.src_group[g])
         return self.Y[-1]
 
     def run(self, X, Ws):
@@ -240,12 +264,16 @@ class ChainStage:
 
     Rank g holds W_g and computes Y_g = Y_{g-1} W_g^T.  Its input buffer and its work queue live in its own memory and are
     mapped into rank g-1, whose GEMM epilogue stores finished tiles straight into that buffer and publishes completed row
-    panels in that queue.  No collective is on the data path.  Re-running needs no host synchronisation between ranks:
-    every ``step`` first resets this rank's queue and then raises a ready flag in rank g-1's memory to the step number;
-    rank g-1's epilogue waits for that value before its first store of the step.
+    panels in that queue.  No collective is on the data path.  Re-running needs no host synchronisation between ranks.
+
+    Every link (input buffer, queue, ready flag) exists twice, used by odd and even steps in turn, so that consecutive
+    steps overlap the way batches stream through a layer pipeline: while this rank still works on step e out of one set,
+    rank g-1 already stores step e+1 into the other.  ``step(e)`` first resets the set of step e+1 (free since this rank's
+    GEMM of step e-1, which precedes it in stream order) and raises that set's ready flag in rank g-1's memory to e+1;
+    rank g-1's epilogue waits for that value before its first store of step e+1.  At most two steps are in flight per link.
     """
 
-    def __init__(self, M, K, widths, rank, world, device, group=None, cfg=3, group_rows=8, scoreboard="rowpanel"):
+    def __init__(self, M, K, widths, rank, world, device, group=None, cfg=3, group_rows=8, scoreboard="rowpanel", consumer_group="auto"):
         from ctapp.symm import symm_empty, view_ptr
         assert len(widths) == world
         self.ext = load()
@@ -254,22 +282,21 @@ class ChainStage:
         self.rowpanel = int(scoreboard == "rowpanel")
         self.ext.preload(self.dev.index)
         BM, BN = _tile(self.ext, cfg)
+        self.src_group = 0 if rank == 0 else (consumer_window(group_rows, self.rowpanel, BM, BM) if consumer_group == "auto" else int(consumer_group))
         plan = stage_plan(M, K, widths, rank, (BM, BN))
         tm = plan["tiles_m"]
         self.k_in, self.n_out, self.tn, self.ntiles = plan["k_in"], plan["n_out"], plan["tiles_n"], plan["ntiles"]
         first, last = plan["first"], plan["last"]
-        # symmetric buffers (collective, same order on every rank)
-        self.Yin, h_y = symm_empty((M, self.k_in) if not first else (8,), torch.bfloat16, self.dev, group, rank)
-        self.entries_sym, h_e = symm_empty((self.ntiles,), torch.int32, self.dev, group, rank)
-        self.ctl, h_c = symm_empty((4,), torch.int32, self.dev, group, rank)       # [head, tail, ready, -]
-        self._hdls = (h_y, h_e, h_c)
-        self.head, self.tail, self.ready = self.ctl[0:1], self.ctl[1:2], self.ctl[2:3]
+        # symmetric buffers (collective, same order on every rank); leading dimension 2 = the set of odd / even steps
+        self.Yin2, h_y = symm_empty((2, M, self.k_in) if not first else (8,), torch.bfloat16, self.dev, group, rank)
+        self.entries_sym, h_e = symm_empty((2, self.ntiles), torch.int32, self.dev, group, rank)
+        self.ctl, h_c = symm_empty((2, 4), torch.int32, self.dev, group, rank)       # per set: [head, tail, ready, -]
+        self._hdls = (h_y, h_e, h_c)   # all three arrive zero-filled; peers may write flags into ctl from here on
         if first:
-            self.entries = producer_order(self.ntiles, self.tn, group_rows).to(self.dev)
-            self.tail.fill_(self.ntiles)
+            self.entries0 = producer_order(self.ntiles, self.tn, group_rows).to(self.dev)
+            self.ctl[:, 1] = self.ntiles
         else:
-            self.entries = self.entries_sym
-            self.entries.fill_(EMPTY)
+            self.entries_sym.fill_(EMPTY)
         self.status = new_status(self.dev)
         self.epoch = 0
         if not last:
@@ -280,31 +307,60 @@ class ChainStage:
             self.dep_off, self.dep_cons = off.to(self.dev), cons.to(self.dev)
             self.sb_pristine = sb.to(self.dev); self.sb = self.sb_pristine.clone()
             nxt = rank + 1
-            self.Yout = view_ptr(h_y.buffer_ptrs[nxt], (M, self.n_out), torch.bfloat16, self.dev)
-            self.dst_entries = view_ptr(h_e.buffer_ptrs[nxt], (tm * tn2,), torch.int32, self.dev)
-            ctl_next = view_ptr(h_c.buffer_ptrs[nxt], (4,), torch.int32, self.dev)
-            self.dst_head, self.dst_tail = ctl_next[0:1], ctl_next[1:2]
+            self.Yout2 = view_ptr(h_y.buffer_ptrs[nxt], (2, M, self.n_out), torch.bfloat16, self.dev)
+            self.dst_entries2 = view_ptr(h_e.buffer_ptrs[nxt], (2, tm * tn2), torch.int32, self.dev)
+            self.dst_ctl2 = view_ptr(h_c.buffer_ptrs[nxt], (2, 4), torch.int32, self.dev)
         else:
             self.tn2 = 0
             self.dep_off = self.dep_cons = self.sb = self.sb_pristine = None
-            self.Yout = torch.empty(M, self.n_out, dtype=torch.bfloat16, device=self.dev)
-            self.dst_entries = self.dst_head = self.dst_tail = None
-        self.up_ready = None if first else view_ptr(h_c.buffer_ptrs[rank - 1], (4,), torch.int32, self.dev)[2:3]
+            self.Yout2 = torch.empty(1, M, self.n_out, dtype=torch.bfloat16, device=self.dev)
+            self.dst_entries2 = self.dst_ctl2 = None
+        self.up_ctl2 = None if first else view_ptr(h_c.buffer_ptrs[rank - 1], (2, 4), torch.int32, self.dev)
+        self._reset_set(1)   # step 1 runs out of set 1
         torch.cuda.synchronize(self.dev)
+
+    def _queue(self, s):
+        """(entries, head, tail) this rank's GEMM pops in a step of set ``s``; rank 0 pops its fixed producer order."""
+        if self.rank == 0:
+            return self.entries0, self.ctl[0, 0:1], self.ctl[0, 1:2]
+        return self.entries_sym[s], self.ctl[s, 0:1], self.ctl[s, 1:2]
+
+    def _reset_set(self, e):
+        """Reset this rank's queue of set e % 2 for step ``e`` and tell rank g-1 it may store that step; restores the
+        scoreboard of the outgoing link on the way (the GEMM enqueued next is its only user)."""
+        first = self.rank == 0
+        s = e & 1
+        entries, head, tail = self._queue(s)
+        with torch.cuda.device(self.dev):
+            self.ext.chain_reset(None if first else entries, head, tail, self.sb, self.sb_pristine,
+                                 ready_flag=None if first else self.up_ctl2[s, 2:3], ready_value=e)
+
+    @property
+    def Yin(self):
+        """Input buffer of the step enqueued last (rank 0 has none)."""
+        return None if self.rank == 0 else self.Yin2[self.epoch & 1]
+
+    @property
+    def Yout(self):
+        """Where the step enqueued last put its output: the next rank's input buffer of that step, or a local tensor."""
+        return self.Yout2[(self.epoch & 1) if self.rank + 1 < self.world else 0]
 
     def step(self, W, X=None):
         """Enqueue one run of this stage.  Rank 0 passes the chain's input X; the other ranks read their input buffer."""
         self.epoch += 1
         e = self.epoch
+        s = e & 1
         first, last = self.rank == 0, self.rank == self.world - 1
+        self._reset_set(e + 1)
+        entries, head, tail = self._queue(s)
         with torch.cuda.device(self.dev):
-            self.ext.chain_reset(None if first else self.entries, self.head, self.tail, self.sb, self.sb_pristine,
-                                 ready_flag=self.up_ready, ready_value=e)
-            inp = X if first else self.Yin
-            self.ext.ctapp_gemm(inp, W, self.Yout, self.cfg, self.entries, self.head, self.tail, self.dep_off, self.dep_cons, self.sb,
-                                self.dst_entries, self.dst_head, self.dst_tail, self.tn, 0, 1, tiles_n2=self.tn2, rowpanel=self.rowpanel,
-                                status=self.status, dst_ready=None if last else self.ready, ready_value=e)
-        return self.Yout
+            inp = X if first else self.Yin2[s]
+            out = self.Yout2[0 if last else s]
+            self.ext.ctapp_gemm(inp, W, out, self.cfg, entries, head, tail, self.dep_off, self.dep_cons, self.sb,
+                                None if last else self.dst_entries2[s], None if last else self.dst_ctl2[s, 0:1],
+                                None if last else self.dst_ctl2[s, 1:2], self.tn, 0, 1, tiles_n2=self.tn2, rowpanel=self.rowpanel,
+                                status=self.status, dst_ready=None if last else self.ctl[s, 2:3], ready_value=e, src_group=self.src_group)
+        return out
 
     def check(self):
         torch.cuda.synchronize(self.dev)

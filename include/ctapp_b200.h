@@ -85,6 +85,10 @@ typedef struct ctapp_chain_args {     /* ctapp.cuh:7-19 */
   int ready_value;
   int* status;                        /* CTAPP_STATUS_INTS ints or NULL */
   int sms;                            /* CTAs to launch, 0 = all SMs */
+  int src_group;                      /* > 1: pop the source queue in windows of src_group published row panels, n-tile
+                                         major inside a window (the L2-friendly order of a producer that finishes row
+                                         panels in groups of that size); 0 | 1 = queue order.  No counterpart in the
+                                         reference, whose consumer pops in queue order (ctapp.cuh:32-48). */
 } ctapp_chain_args;
 
 /* One stage of the chain: Y = X * W^T with tile ids popped from args->src and completion published into args->dst.

@@ -116,3 +116,40 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
             fails.append(f"M={M}: flags != epoch {bd.epoch}")
         _sync(dev)
     return fails
+
+
+def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg):
+    """One chain stage per process, ``steps`` steps enqueued back to back with a different input each and no host
+    synchronisation in between: consecutive steps overlap on the doubled links, and every step's output at the last stage
+    must still be the CPU oracle's chain of that step's input."""
+    import sys, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    from oracle import chain as oc
+    from ctapp.pipeline import ChainStage
+    fails = []
+    Xs, Ws = [], None
+    for e in range(steps):
+        X, Ws_e = oc.make_chain_inputs(M, NK, [NK] * world, seed=e)
+        Xs.append(X)
+        Ws = Ws or Ws_e
+    stage = ChainStage(M, NK, [NK] * world, rank, world, dev, group=None, cfg=cfg, group_rows=2)
+    Wmine = Ws[rank].to(dev)
+    Xd = [x.to(dev) for x in Xs] if rank == 0 else [None] * steps
+    outs = []
+    for e in range(steps):
+        y = stage.step(Wmine, Xd[e])
+        if rank == world - 1:
+            outs.append(y.clone())      # stream order: after this step's kernel, before the next one overwrites the output
+    stage.check()
+    _sync(dev)
+    if rank == world - 1:
+        for e in range(steps):
+            ref = oc.chain_reference(Xs[e], Ws)
+            mx, mean = oc.error_stats(outs[e].cpu(), ref)
+            if not (mx <= 2e-2 and mean <= 1e-3):
+                fails.append(f"step {e}: max {mx:.3e} mean {mean:.3e}")
+    if stage.epoch != steps:
+        fails.append(f"epoch {stage.epoch} != {steps}")
+    return fails

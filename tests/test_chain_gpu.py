@@ -217,3 +217,17 @@ def test_clock_offset_and_chain_timeline_two_gpus():
     assert c["first_tile_min_us"] > p["first_tile_min_us"] + 5, (p, c)     # nothing to consume before the first panel is published
     assert c["exit_max_us"] > p["exit_max_us"], (p, c)
     assert c["first_tile_min_us"] < p["exit_max_us"], "the consumer started only after the producer had finished: no pipelining"
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("cfg", [3, 10])
+def test_chain_stages_one_process_per_gpu_overlapped_steps(cfg):
+    """One stage per process (the form ``bench.py --gpus N`` runs): five steps with different inputs enqueued back to back;
+    the doubled links let step e+1 enter a link while step e is still being consumed, and every step's result must be
+    the oracle's."""
+    import mp_cases
+    from ctapp.tp4 import launch
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg)
+    assert not bad, res
+    assert all(r == [] for r in res), res

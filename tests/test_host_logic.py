@@ -37,6 +37,33 @@ def test_ramped_and_listed_producer_orders():
     assert o[:4].tolist() == [0, 1, 2, 3] and o[4:7].tolist() == [4, 8, 12]      # second group: rows 1-3, n-major
 
 
+@pytest.mark.parametrize("tm,tn,g", [(32, 32, 8), (16, 32, 2), (5, 4, 2), (7, 3, 4), (3, 8, 8), (4, 4, 1), (4, 4, 0)])
+def test_consumer_pop_windows_are_a_permutation_in_n_major_order(tm, tn, g):
+    """The i-th pop of a consuming stage reads slot pop_slots[i]: every slot exactly once; inside a window of g published
+    row panels the pops take slot j of every panel before slot j+1; when the producer publishes its groups in order, the
+    resulting tile order is the producer's own grouped order."""
+    from ctapp.pipeline import consumer_window, pop_slots, producer_order
+    n = tm * tn
+    slots = pop_slots(n, tn, g).numpy()
+    assert sorted(slots.tolist()) == list(range(n))
+    if g <= 1:
+        assert slots.tolist() == list(range(n))
+        return
+    panel, j = slots // tn, slots % tn
+    for w0 in range(0, tm, g):
+        gw = min(g, tm - w0)
+        sel = (panel >= w0) & (panel < w0 + gw)
+        idx = np.nonzero(sel)[0]
+        assert idx.min() == w0 * tn and idx.max() == (w0 + gw) * tn - 1          # a window's pops are consecutive
+        assert np.array_equal(j[idx], np.repeat(np.arange(tn), gw))              # n-tile major ...
+        assert np.array_equal(panel[idx], np.tile(np.arange(w0, w0 + gw), tn))   # ... over the window's panels
+    # queue filled panel by panel in ascending order (entry = panel * tn + j): tiles come out in the grouped producer order
+    if tm % g == 0:
+        assert np.array_equal(slots, producer_order(n, tn, g).numpy())
+    assert consumer_window(8, 1, 256, 256) == 8 and consumer_window(8, 1, 128, 256) == 4 and consumer_window(2, 1, 128, 256) == 0
+    assert consumer_window("ramp", 1, 256, 256) == 0 and consumer_window(8, 0, 256, 256) == 0 and consumer_window(0, 1, 128, 128) == 0
+
+
 def test_boundary_tail_rule_matches_oracle():
     """``CtappBoundary._tail`` (host logic, no GPU needed for the rule itself) against the oracle's statement of it."""
     from oracle import boundary as ob

@@ -9,6 +9,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "gemm_sm100.cuh"
@@ -53,14 +54,16 @@ struct DeviceGuard {
   DeviceGuard g_(dev); \
   if (!g_.ok) return fail(-2, "cannot select device %d", dev)
 
-static long long g_limit_ms = -1;
+static std::atomic<long long> g_limit_ms{-1};   // entry points may be called from several host threads
 static long long limit_ns() {
-  if (g_limit_ms < 0) {
+  long long ms = g_limit_ms.load(std::memory_order_relaxed);
+  if (ms < 0) {
     const char* e = getenv("CTAPP_WAIT_LIMIT_MS");
-    g_limit_ms = e ? atoll(e) : 2000;
-    if (g_limit_ms <= 0) g_limit_ms = 2000;
+    ms = e ? atoll(e) : 2000;
+    if (ms <= 0) ms = 2000;
+    g_limit_ms.store(ms, std::memory_order_relaxed);
   }
-  return g_limit_ms * 1000000ll;
+  return ms * 1000000ll;
 }
 
 // ------------------------------------------------------------------------------------------ driver entry points
@@ -107,10 +110,11 @@ static int cfg_bn(int id) {
 }
 static bool cfg_pair(int id) { return id == 10; }
 static int sm_count(int dev) {
-  static int cache[64];
+  static std::atomic<int> cache[64];
   if (dev < 0 || dev >= 64) return 0;
-  if (!cache[dev]) cudaDeviceGetAttribute(&cache[dev], cudaDevAttrMultiProcessorCount, dev);
-  return cache[dev];
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (!n && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
 template <int BN> static int prepare_kernel() {
   CU_OK(cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes));

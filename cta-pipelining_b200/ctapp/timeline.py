@@ -67,3 +67,75 @@ def chain_timeline(chain):
                     "exit_min_us": us(t[:, 7].min()), "exit_max_us": us(t[:, 7].max()),
                     "tiles_per_cta_median": float(statistics.median(s[:, 5].tolist()))})
     return out
+
+
+_SEGMENTS = (("wait for the first tile", 0, 1, "#bdbdbd"), ("main loops", 1, 2, "#3b6fb6"),
+             ("last epilogue", 2, 3, "#4daf4a"), ("publish and exit", 3, 7, "#ff7f00"))
+
+
+def gantt_svg(stages, path=None, width=1200, row_h=3, title="CTA timeline"):
+    """Gantt chart of per-CTA stamps as an SVG document (reference bench/timeline.py:119-160 draws the same picture with
+    matplotlib, which this library does not depend on).
+
+    ``stages``: list of (label, stamps, offset_ns): ``stamps`` an (n, 8) integer array or tensor in the kernels' slot layout
+    (rows with entry == 0 are CTAs that did not run), ``offset_ns`` what to add to put them on the first stage's clock.
+    One row per CTA, stages stacked top to bottom, rows ordered by SM id; colours: grey = waiting for the first tile,
+    blue = first tile acquired to last main loop issued, green = last epilogue, orange = publish and exit.
+    Returns the SVG text and writes it to ``path`` when given."""
+    rows, t0, t1 = [], None, None
+    for label, st, off in stages:
+        s = torch.as_tensor(st).reshape(-1, 8).double()
+        s = s[s[:, 0] > 0]
+        s = s[torch.argsort(s[:, 6], stable=True)]
+        for r in s.tolist():
+            t = [v + off if (k in (0, 1, 2, 3, 4, 7) and v > 0) else v for k, v in enumerate(r)]
+            rows.append((label, t))
+            t0 = t[0] if t0 is None else min(t0, t[0])
+            t1 = t[7] if t1 is None else max(t1, t[7])
+    if not rows:
+        raise ValueError("no CTA left a stamp")
+    span = max(t1 - t0, 1.0)
+    left, top = 90, 30
+    x = lambda v: left + (v - t0) / span * (width - left - 10)  # noqa: E731
+    height = top + len(rows) * row_h + 40
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="monospace" font-size="11">',
+           f'<text x="{left}" y="14">{title}: {span / 1e3:.1f} us, {len(rows)} CTAs</text>']
+    y, prev = top, None
+    for label, t in rows:
+        if label != prev:
+            out.append(f'<text x="2" y="{y + 10}">{label}</text>')
+            prev = label
+        for _, a, b, colour in _SEGMENTS:
+            ta, tb = t[a], t[b]
+            if a == 1 and ta <= 0:        # a CTA that never got a tile: grey from entry to exit
+                continue
+            if ta > 0 and tb > ta:
+                out.append(f'<rect x="{x(ta):.1f}" y="{y}" width="{max(x(tb) - x(ta), 0.3):.1f}" height="{row_h}" fill="{colour}"/>')
+        if t[1] <= 0:
+            out.append(f'<rect x="{x(t[0]):.1f}" y="{y}" width="{max(x(t[7]) - x(t[0]), 0.3):.1f}" height="{row_h}" fill="#bdbdbd"/>')
+        y += row_h
+    for i in range(6):
+        v = t0 + span * i / 5
+        out.append(f'<text x="{x(v) - 10:.0f}" y="{y + 14}">{(v - t0) / 1e3:.0f}</text>')
+    lx = left
+    for name, _, _, colour in _SEGMENTS:
+        out.append(f'<rect x="{lx}" y="{y + 22}" width="10" height="10" fill="{colour}"/><text x="{lx + 14}" y="{y + 31}">{name}</text>')
+        lx += 14 + 8 * len(name) + 20
+    out.append("</svg>")
+    text = "\n".join(out)
+    if path:
+        with open(path, "w") as f:
+            f.write(text)
+    return text
+
+
+def chain_gantt_svg(chain, path=None):
+    """``gantt_svg`` of the most recent run of a ``Chain`` built with ``stamps=True`` (clock offsets measured here)."""
+    assert chain.stamps, "build the Chain with stamps=True"
+    for d in chain.devs:
+        torch.cuda.synchronize(d)
+    stages = []
+    for g, st in enumerate(chain.stamps):
+        off = 0.0 if g == 0 else clock_offset(chain.devs[0].index, chain.devs[g].index)[0]
+        stages.append((f"stage {g} gpu {chain.devs[g].index}", st.cpu(), off))
+    return gantt_svg(stages, path, title=f"{len(stages)}-stage chain, M={chain.M}")

@@ -94,6 +94,22 @@ def test_chain_three_stages_one_gpu():
     assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
 
 
+def test_gantt_of_a_one_gpu_chain_run():
+    """Stamps of a two-stage run on one GPU drawn as SVG: every CTA of both stages gets a row."""
+    import xml.dom.minidom
+    from ctapp.pipeline import Chain
+    from ctapp.timeline import chain_gantt_svg
+    M, K, N = 1024, 1024, 2048
+    ch = Chain(M, K, [N, N], [0, 0], cfg=10, group_rows=2, stamps=True)
+    X, Ws = oc.make_chain_inputs(M, K, [N, N], seed=0)
+    ch.run(X.cuda(0), [w.cuda(0) for w in Ws])
+    ch.check()
+    svg = chain_gantt_svg(ch)
+    xml.dom.minidom.parseString(svg)
+    ctas = 2 * min(148 // 2, (M // 256) * (N // 256)) * 2          # CTA pairs that got a tile, both stages
+    assert f"{ctas} CTAs" in svg, svg[:200]
+
+
 def test_missing_producer_times_out_cleanly():
     """Fault injection on the host side: the consumer is launched although nothing will ever fill its queue.  Its bounded
     wait must give up, report code 1 in the status buffer, and leave the context usable."""
@@ -217,6 +233,9 @@ def test_clock_offset_and_chain_timeline_two_gpus():
     assert c["first_tile_min_us"] > p["first_tile_min_us"] + 5, (p, c)     # nothing to consume before the first panel is published
     assert c["exit_max_us"] > p["exit_max_us"], (p, c)
     assert c["first_tile_min_us"] < p["exit_max_us"], "the consumer started only after the producer had finished: no pipelining"
+    from ctapp.timeline import chain_gantt_svg
+    svg = chain_gantt_svg(ch)
+    assert svg.count("<rect") >= 2 * 148 * 3 and "stage 1 gpu 1" in svg
 
 
 @pytest.mark.multigpu(2)

@@ -74,3 +74,22 @@ def test_boundary_tail_rule_matches_oracle():
             fake = types.SimpleNamespace(down_tail=down_tail, down_raster=raster, down_swizzle=swz, n1=8192)
             want = down_tail if down_tail != "auto" else ob.tail_cols(M, raster, swz)
             assert CtappBoundary._tail(fake, M) == want
+
+
+def test_gantt_svg_from_synthetic_stamps(tmp_path):
+    """The Gantt writer needs no GPU: rows = CTAs that ran, ordered by SM id, second stage shifted by its clock offset."""
+    import torch
+    import xml.dom.minidom
+    from ctapp.timeline import gantt_svg
+    a = torch.zeros(4, 8, dtype=torch.int64)
+    a[0] = torch.tensor([1000, 1100, 5000, 5200, 5300, 7, 3, 5400])
+    a[1] = torch.tensor([1005, 1110, 5100, 5300, 5400, 7, 1, 5500])
+    a[2] = torch.tensor([1010, 0, 0, 0, 0, 0, 2, 1500])             # never got a tile
+    b = torch.zeros(2, 8, dtype=torch.int64)
+    b[0] = torch.tensor([90000, 91000, 95000, 95100, 0, 7, 0, 95200])  # other GPU's clock: 88 500 ns ahead
+    text = gantt_svg([("stage 0", a, 0.0), ("stage 1", b, -88500.0)], str(tmp_path / "g.svg"))
+    doc = xml.dom.minidom.parseString(text)
+    assert doc.documentElement.tagName == "svg"
+    assert "4 CTAs" in text and "stage 0" in text and "stage 1" in text
+    assert text.count("<rect") == 3 * 4 + 1 + 4               # four segments for each of the 3 CTAs that worked, one idle row, legend
+    assert (tmp_path / "g.svg").read_text() == text

@@ -25,8 +25,9 @@ def main():
     ap.add_argument("--ms", default="1024,2048,4096,8192,16384,32768")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--cfg", type=int, default=10)
-    ap.add_argument("--groups", default="1,2,4")
+    ap.add_argument("--groups", default="1,2,4,ramp")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--skip-baselines", action="store_true", help="only the ideal, this library on one GPU and the pipelined chain")
     a = ap.parse_args()
     assert torch.cuda.device_count() >= 2, "needs 2 GPUs"
     g = torch.Generator().manual_seed(0)
@@ -42,16 +43,17 @@ def main():
         r["ideal_us"] = r["one_gpu_cublas_us"] / 2
         ours1 = mt.OneGpuTma(M, X, W1a, W2a, a.cfg)
         r["one_gpu_ours_us"] = measure(ours1, a.reps, devs=(0,))[0]
-        best = None
+        best, tp = None, None
         for chunk in (256, 512, 1024, 2048, 4096, 8192, 16384, 32768):
-            if chunk > M:
+            if chunk > M or a.skip_baselines:
                 break
             t = measure(mt.MicroBatchCublas(M, X, W1a, W2b, chunk), a.reps)[0]
             if best is None or t < best[0]:
                 best = (t, chunk)
-        r["microbatch_cublas_us"], r["microbatch_chunk"] = best
-        tp = mt.TensorParallel2(M, X, W1a, W2b)
-        r["tp2_cublas_nccl_us"] = measure(tp, a.reps)[0]
+        if not a.skip_baselines:
+            r["microbatch_cublas_us"], r["microbatch_chunk"] = best
+            tp = mt.TensorParallel2(M, X, W1a, W2b)
+            r["tp2_cublas_nccl_us"] = measure(tp, a.reps)[0]
         bestc = None
         for gr in [v if v == "ramp" else int(v) for v in a.groups.split(",")]:
             c = mt.Ctapp(M, X, W1a, W2b, a.cfg, a.cfg, gr)
@@ -62,8 +64,9 @@ def main():
                 bestc = (t, gr)
         r["ctapp_us"], r["ctapp_group_rows"] = bestc
         r["ctapp_over_ideal"] = r["ctapp_us"] / r["ideal_us"]
-        r["reduction_vs_microbatch_pct"] = 100 * (1 - r["ctapp_us"] / r["microbatch_cublas_us"])
-        r["reduction_vs_tp_pct"] = 100 * (1 - r["ctapp_us"] / r["tp2_cublas_nccl_us"])
+        if not a.skip_baselines:
+            r["reduction_vs_microbatch_pct"] = 100 * (1 - r["ctapp_us"] / r["microbatch_cublas_us"])
+            r["reduction_vs_tp_pct"] = 100 * (1 - r["ctapp_us"] / r["tp2_cublas_nccl_us"])
         r["chain_tflops"] = 2 * 2 * M * N * K / (r["ctapp_us"] * 1e-6) / 1e12
         print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in r.items()}), flush=True)
         rows.append(r)

@@ -386,6 +386,8 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   p.tiles_n2 = a->tiles_n2; p.rowpanel = a->rowpanel; p.skip_wait = a->skip_wait;
   ARG(a->src_group >= 0 && a->src_group <= 1024, "bad src_group %d", a->src_group);
   p.src_group = a->src_group;
+  ARG(!a->src_windows || a->n_windows > 0, "src_windows needs n_windows > 0");
+  p.src_windows = a->src_windows; p.n_windows = a->src_windows ? a->n_windows : 0;
   p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
   p.status = a->status; p.stamps = a->stamps;
   if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream));

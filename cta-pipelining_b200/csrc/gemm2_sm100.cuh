@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
       int k_static = 0, ntiles_done = 0;
       uint32_t armed = 0, armed_parity = 0;
       uint32_t panel_seen[4] = {0, 0, 0, 0};
+      int win_cur = 0;
       auto pop = [&]() -> int {
         if (p.mode == kModeChain) { const int idx = atomicAdd(p.src.head, 1); return idx < p.num_tiles ? idx : -1; }
         const int idx = pair + (k_static++) * npairs;
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           if (tile >= 0 && p.status && ld_relaxed_gpu(p.status) != 0) tile = -1;
           if (tile >= 0 && p.mode == kModeChain && !p.skip_wait) {
             int seen;
-            const int slot = queue_slot(p, tile);
+            const int slot = queue_slot(p, tile, win_cur);
             if (!spin_acquire_sys(p.src.entries + slot, PredNe{-1}, limit, seen)) {
               report_status(p.status, kStatusTimeoutQueue, slot, 0, seen); abort_pair(kStatusTimeoutQueue); break;
             }

@@ -49,7 +49,8 @@ struct alignas(64) GemmParams {
   const int* dep_consumers;
   int* scoreboard;
   Queue dst;
-  int tiles_n2, rowpanel, skip_wait, src_group;
+  int tiles_n2, rowpanel, skip_wait, src_group, n_windows;
+  const int* src_windows;
   const int* dst_ready;
   int ready_value;
   // tensor-parallel boundary
@@ -80,14 +81,27 @@ template <int BN> struct GemmCfg {
 };
 
 // Chain mode: which slot of the source queue the idx-th pop reads.  The producer publishes a finished row panel as tiles_n
-// consecutive slots.  With src_group = g > 1 the pops walk windows of g such panels n-tile major (slot 0 of every panel of the
-// window, then slot 1, ...), so that g row panels share each weight tile while it is hot in L2; the last window takes the
-// panels that are left.  A permutation of the slots: every slot is still read exactly once.
-__device__ __forceinline__ int queue_slot(const GemmParams& p, int idx) {
-  const int tn = p.tiles_n, g = p.src_group;
-  if (g <= 1) return idx % p.src.cap;
-  const int wsz = g * tn, base = (idx / wsz) * wsz, left = (p.src.cap - base) / tn;
-  const int gw = left < g ? left : g, r = idx - base;
+// consecutive slots.  With windows the pops walk a window of g such panels n-tile major (slot 0 of every panel of the
+// window, then slot 1, ...), so that g row panels share each weight tile while it is hot in L2.  src_group = g > 1: windows of
+// constant size (the last one takes the panels that are left); src_windows: n_windows + 1 ascending panel offsets of windows
+// of any sizes.  A permutation of the slots either way: every slot is still read exactly once.  `cur` is the caller's
+// cursor into src_windows (pops of one CTA ascend).
+__device__ __forceinline__ int queue_slot(const GemmParams& p, int idx, int& cur) {
+  const int tn = p.tiles_n;
+  int first, gw;   // first panel and panel count of the window idx falls into
+  if (p.src_windows) {
+    const int pi = idx / tn;
+    while (cur + 1 < p.n_windows && __ldg(p.src_windows + cur + 1) <= pi) cur++;
+    first = __ldg(p.src_windows + cur);
+    gw = __ldg(p.src_windows + cur + 1) - first;
+  } else {
+    const int g = p.src_group;
+    if (g <= 1) return idx % p.src.cap;
+    first = (idx / (g * tn)) * g;
+    const int left = p.src.cap / tn - first;
+    gw = left < g ? left : g;
+  }
+  const int base = first * tn, r = idx - base;
   return base + (r % gw) * tn + r / gw;
 }
 
@@ -161,6 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       uint32_t armed = 0, armed_parity = 0;   // per stage: has a load been issued, and in which phase
       int k_static = 0, ntiles_done = 0;
       uint32_t panel_seen[4] = {0, 0, 0, 0};
+      int win_cur = 0;
       auto pop = [&]() -> int {
         if (p.mode == kModeChain) { const int idx = atomicAdd(p.src.head, 1); return idx < p.num_tiles ? idx : -1; }
         const int idx = static_cast<int>(blockIdx.x) + (k_static++) * static_cast<int>(gridDim.x);
@@ -173,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (tile >= 0 && p.status && ld_relaxed_gpu(p.status) != 0) tile = -1;   // another CTA gave up: stop taking work
         if (tile >= 0 && p.mode == kModeChain && !p.skip_wait) {
           int seen;
-          const int slot = queue_slot(p, tile);
+          const int slot = queue_slot(p, tile, win_cur);
           if (!spin_acquire_sys(p.src.entries + slot, PredNe{-1}, limit, seen)) {
             report_status(p.status, kStatusTimeoutQueue, slot, 0, seen); *s_abort = kStatusTimeoutQueue; break;
           }

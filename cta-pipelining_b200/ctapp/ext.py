@@ -76,7 +76,8 @@ class ChainArgs(C.Structure):
     _fields_ = [("stamps", C.c_void_p), ("src", Queue), ("dep_offsets", C.c_void_p), ("dep_consumers", C.c_void_p),
                 ("scoreboard", C.c_void_p), ("dst", Queue), ("tiles_n", C.c_int), ("skip_wait", C.c_int), ("fence", C.c_int),
                 ("tiles_n2", C.c_int), ("rowpanel", C.c_int), ("dst_ready", C.c_void_p), ("ready_value", C.c_int),
-                ("status", C.c_void_p), ("sms", C.c_int), ("src_group", C.c_int)]
+                ("status", C.c_void_p), ("sms", C.c_int), ("src_group", C.c_int),
+                ("src_windows", C.c_void_p), ("n_windows", C.c_int)]
 
 
 class TpDownArgs(C.Structure):
@@ -239,7 +240,7 @@ class ChainModule:
 
     def ctapp_gemm(self, X, W, Y, config_id, src_entries, src_head, src_tail, dep_offsets, dep_consumers, scoreboard,
                    dst_entries, dst_head, dst_tail, tiles_n, skip_wait, fence, stamps=None, tiles_n2=0, rowpanel=0,
-                   status=None, dst_ready=None, ready_value=0, sms=0, src_group=0):
+                   status=None, dst_ready=None, ready_value=0, sms=0, src_group=0, src_windows=None):
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
         M, K = X.shape
         N = W.shape[0]
@@ -255,6 +256,8 @@ class ChainModule:
         a.tiles_n, a.skip_wait, a.fence, a.tiles_n2, a.rowpanel = int(tiles_n), int(skip_wait), int(fence), int(tiles_n2), int(rowpanel)
         a.dst_ready, a.ready_value = _ptr(dst_ready), int(ready_value)
         a.status, a.sms, a.src_group = _ptr(status), int(sms), int(src_group)
+        if src_windows is not None:      # int32 device tensor of window offsets in row panels: [0, ..., panels]
+            a.src_windows, a.n_windows = _ptr(_i32(src_windows, "src_windows")), src_windows.numel() - 1
         dev = X.device.index
         _check(self.lib.ctapp_chain_gemm(_ptr(X), _ptr(W), _ptr(Y), M, N, K, int(config_id), C.byref(a), dev, _stream(dev)))
 

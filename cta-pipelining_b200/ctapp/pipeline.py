@@ -97,24 +97,45 @@ def _tile(ext, cfg):
 
 
 def pop_slots(ntiles, tn, group):
-    """Queue slot read by the i-th pop of a consuming stage (host model of the kernel's ``queue_slot``): windows of ``group``
-    published row panels, n-tile major inside a window; the last window takes the panels that are left.  group <= 1: queue order."""
+    """Queue slot read by the i-th pop of a consuming stage (host model of the kernel's ``queue_slot``): windows of published
+    row panels, n-tile major inside a window.  ``group``: an int = windows of that many panels (the last one takes the panels
+    that are left; <= 1: queue order), or a list of window sizes summing to the number of row panels."""
     idx = torch.arange(ntiles)
-    if group <= 1:
-        return idx.int()
-    wsz = group * tn
-    base = (idx // wsz) * wsz
-    gw = torch.clamp((ntiles - base) // tn, max=group)
+    if isinstance(group, int):
+        if group <= 1:
+            return idx.int()
+        tm = ntiles // tn
+        group = [group] * (tm // group) + ([tm % group] if tm % group else [])
+    sizes = torch.tensor(list(group))
+    assert int(sizes.sum()) * tn == ntiles and bool((sizes > 0).all()), (group, ntiles, tn)
+    first = torch.cumsum(sizes, 0) - sizes
+    w = torch.repeat_interleave(torch.arange(len(sizes)), sizes * tn)      # window of every pop
+    base, gw = first[w] * tn, sizes[w]
     r = idx - base
     return (base + (r % gw) * tn + r // gw).int()
 
 
-def consumer_window(group_rows, rowpanel, bm_prev, bm):
-    """Window (in this stage's row panels) a consuming stage pops in: the rows its producer finishes together."""
-    if not rowpanel or not isinstance(group_rows, int) or group_rows <= 0:
+def consumer_window(group_rows, rowpanel, bm_prev, bm, tm=0):
+    """How a consuming stage pops its queue, given the order its producer works in: an int (constant windows of that many of
+    this stage's row panels; 0 = queue order) or, for a producer with varying groups ("ramp" or a list), the list of window
+    sizes.  The windows are the row panels the producer finishes together."""
+    if not rowpanel or not group_rows:
         return 0
-    g = group_rows * bm_prev // bm
-    return g if g > 1 else 0
+    if isinstance(group_rows, int):
+        g = group_rows * bm_prev // bm
+        return g if g > 1 else 0
+    if bm_prev != bm:
+        return 0
+    return ramp_groups(tm) if group_rows == "ramp" else list(group_rows)
+
+
+def _window_args(win, dev):
+    """(src_group, src_windows tensor or None) for the bindings."""
+    if isinstance(win, int):
+        return win, None
+    off = torch.zeros(len(win) + 1, dtype=torch.int32)
+    off[1:] = torch.cumsum(torch.tensor(win), 0)
+    return 0, off.to(dev)
 
 
 class Pipeline:
@@ -175,8 +196,9 @@ class Chain:
         tiles = [_tile(self.ext, c) for c in self.cfg]
         i32 = dict(dtype=torch.int32)
         L = len(self.widths)
-        self.src_group = [0] + [consumer_window(group_rows, self.rowpanel, tiles[g - 1][0], tiles[g][0]) if consumer_group == "auto"
-                                else int(consumer_group) for g in range(1, L)]
+        wins = [0] + [consumer_window(group_rows, self.rowpanel, tiles[g - 1][0], tiles[g][0], -(-M // tiles[g][0])) if consumer_group == "auto"
+                      else consumer_group for g in range(1, L)]
+        self.src_group, self.src_windows = zip(*[_window_args(w, self.devs[g]) for g, w in enumerate(wins)])
         self.tn = [-(-n // t[1]) for n, t in zip(self.widths, tiles)]
         self.ntiles = [-(-M // t[0]) * tn for t, tn in zip(tiles, self.tn)]
         self.entries, self.head, self.tail, self.Y, self.status = [], [], [], [], []
@@ -227,7 +249,7 @@ class Chain:
                                     None if last else self.entries[g + 1], None if last else self.head[g + 1],
                                     None if last else self.tail[g + 1], self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
                                     tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms,
-                                    stamps=self.stamps[g] if self.stamps else None, src_group=self.src_group[g])
+                                    stamps=self.stamps[g] if self.stamps else None, src_group=self.src_group[g], src_windows=self.src_windows[g])
         return self.Y[-1]
 
     def run(self, X, Ws):
@@ -282,7 +304,8 @@ class ChainStage:
         self.rowpanel = int(scoreboard == "rowpanel")
         self.ext.preload(self.dev.index)
         BM, BN = _tile(self.ext, cfg)
-        self.src_group = 0 if rank == 0 else (consumer_window(group_rows, self.rowpanel, BM, BM) if consumer_group == "auto" else int(consumer_group))
+        win = 0 if rank == 0 else (consumer_window(group_rows, self.rowpanel, BM, BM, -(-M // BM)) if consumer_group == "auto" else consumer_group)
+        self.src_group, self.src_windows = _window_args(win, self.dev)
         plan = stage_plan(M, K, widths, rank, (BM, BN))
         tm = plan["tiles_m"]
         self.k_in, self.n_out, self.tn, self.ntiles = plan["k_in"], plan["n_out"], plan["tiles_n"], plan["ntiles"]
@@ -359,7 +382,7 @@ class ChainStage:
             self.ext.ctapp_gemm(inp, W, out, self.cfg, entries, head, tail, self.dep_off, self.dep_cons, self.sb,
                                 None if last else self.dst_entries2[s], None if last else self.dst_ctl2[s, 0:1],
                                 None if last else self.dst_ctl2[s, 1:2], self.tn, 0, 1, tiles_n2=self.tn2, rowpanel=self.rowpanel,
-                                status=self.status, dst_ready=None if last else self.ctl[s, 2:3], ready_value=e, src_group=self.src_group)
+                                status=self.status, dst_ready=None if last else self.ctl[s, 2:3], ready_value=e, src_group=self.src_group, src_windows=self.src_windows)
         return out
 
     def check(self):

@@ -89,6 +89,10 @@ typedef struct ctapp_chain_args {     /* ctapp.cuh:7-19 */
                                          major inside a window (the L2-friendly order of a producer that finishes row
                                          panels in groups of that size); 0 | 1 = queue order.  No counterpart in the
                                          reference, whose consumer pops in queue order (ctapp.cuh:32-48). */
+  const int* src_windows;             /* device array of n_windows + 1 ascending row-panel offsets (first 0, last = row
+                                         panels of this GEMM): windows of any sizes, for a producer that finishes its
+                                         row panels in groups of varying size; overrides src_group.  NULL = off. */
+  int n_windows;
 } ctapp_chain_args;
 
 /* One stage of the chain: Y = X * W^T with tile ids popped from args->src and completion published into args->dst.

@@ -118,7 +118,7 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     return fails
 
 
-def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg):
+def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg, group_rows=2):
     """One chain stage per process, ``steps`` steps enqueued back to back with a different input each and no host
     synchronisation in between: consecutive steps overlap on the doubled links, and every step's output at the last stage
     must still be the CPU oracle's chain of that step's input."""
@@ -134,7 +134,7 @@ def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg):
         X, Ws_e = oc.make_chain_inputs(M, NK, [NK] * world, seed=e)
         Xs.append(X)
         Ws = Ws or Ws_e
-    stage = ChainStage(M, NK, [NK] * world, rank, world, dev, group=None, cfg=cfg, group_rows=2)
+    stage = ChainStage(M, NK, [NK] * world, rank, world, dev, group=None, cfg=cfg, group_rows=group_rows)
     Wmine = Ws[rank].to(dev)
     Xd = [x.to(dev) for x in Xs] if rank == 0 else [None] * steps
     outs = []

@@ -43,6 +43,7 @@ def _run_case(M, K, N1, N2, cfg1, cfg2, devA, devB, runs=3, **kw):
 @pytest.mark.parametrize("case", [(256, 512, 512, 768, 3, 3, {}), (512, 1024, 1024, 1024, 5, 3, dict(group_rows=2)),
                                   (512, 512, 1024, 768, 10, 10, {}), (768, 512, 768, 1024, 10, 3, dict(group_rows=2)), (640, 256, 512, 512, 3, 10, dict(scoreboard="tile")),
                                   (384, 512, 512, 512, 10, 10, dict(group_rows=1)),
+                                  (2048, 512, 512, 768, 3, 3, dict(group_rows="ramp")), (2304, 256, 768, 512, 10, 10, dict(group_rows=[1, 3, 4, 1])),
                                   (384, 512, 768, 512, 3, 5, dict(scoreboard="tile")), (1000, 520, 1000, 264, 5, 5, dict(group_rows=8))])
 def test_chain_one_gpu_small(case):
     M, K, N1, N2, c1, c2, kw = case
@@ -247,6 +248,6 @@ def test_chain_stages_one_process_per_gpu_overlapped_steps(cfg):
     import mp_cases
     from ctapp.tp4 import launch
     world = 4 if torch.cuda.device_count() >= 4 else 2
-    res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg)
+    res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg, 2 if cfg == 3 else "ramp")
     assert not bad, res
     assert all(r == [] for r in res), res

@@ -60,8 +60,14 @@ def test_consumer_pop_windows_are_a_permutation_in_n_major_order(tm, tn, g):
     # queue filled panel by panel in ascending order (entry = panel * tn + j): tiles come out in the grouped producer order
     if tm % g == 0:
         assert np.array_equal(slots, producer_order(n, tn, g).numpy())
+    # windows of varying size follow a ramped producer the same way
+    from ctapp.pipeline import ramp_groups
+    sizes = ramp_groups(tm)
+    assert np.array_equal(pop_slots(n, tn, sizes).numpy(), producer_order(n, tn, sizes).numpy())
+    assert consumer_window("ramp", 1, 256, 256, tm) == sizes and consumer_window([1, tm - 1], 1, 128, 128, tm) == [1, tm - 1]
+    assert consumer_window("ramp", 1, 128, 256, tm) == 0
     assert consumer_window(8, 1, 256, 256) == 8 and consumer_window(8, 1, 128, 256) == 4 and consumer_window(2, 1, 128, 256) == 0
-    assert consumer_window("ramp", 1, 256, 256) == 0 and consumer_window(8, 0, 256, 256) == 0 and consumer_window(0, 1, 128, 128) == 0
+    assert consumer_window(8, 0, 256, 256) == 0 and consumer_window(0, 1, 128, 128) == 0
 
 
 def test_boundary_tail_rule_matches_oracle():

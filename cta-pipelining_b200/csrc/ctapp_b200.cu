@@ -170,7 +170,7 @@ static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t s
   if (pairs > p.num_tiles) pairs = p.num_tiles;
   if (pairs < 1) return 0;
   p.limit_ns = limit_ns();
-  CU_OK(cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(p.act ? gemm2_kernel<true> : gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * pairs);
@@ -189,7 +189,8 @@ static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t s
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel, p));
+  if (p.act) CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<true>, p));
+  else CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<false>, p));
   return 0;
 }
 
@@ -313,7 +314,7 @@ int ctapp_occupancy(int config_id) { return cfg_bn(config_id) ? 1 : fail(-1, "ba
 int ctapp_kernel_info(int which, char* buf, int buf_len) {
   ARG(buf && buf_len > 0, "null buffer");
   cudaFuncAttributes a;
-  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel : (const void*)tp_reduce_kernel<4, 2>;
+  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel<false> : which == 4 ? (const void*)gemm2_kernel<true> : (const void*)tp_reduce_kernel<4, 2>;
   CU_OK(cudaFuncGetAttributes(&a, fn));
   snprintf(buf, buf_len, "regs=%d local=%zu static_smem=%zu max_threads=%d", a.numRegs, a.localSizeBytes, a.sharedSizeBytes, a.maxThreadsPerBlock);
   return 0;
@@ -330,7 +331,9 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 1>));
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
-  CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel));
+  CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false>));
+  CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<true>));
+  CU_OK(cudaFuncGetAttributes(&a, silu_mul_kernel));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<1, false>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, false>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<4, false>));
@@ -340,7 +343,8 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<8, true>));
   if (int r = prepare_kernel<256>()) return r;
   if (int r = prepare_kernel<128>()) return r;
-  CU_OK(cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(gemm2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
   return 0;
 }
 
@@ -451,7 +455,11 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
   GemmParams p;
   if (int r = fill_common(p, a->X, a->W, a->M, a->N, a->K, bn, pair)) return r;
   ARG(a->Y, "null output");
-  if (int r = make_tmap(&p.tmD[0], a->Y, a->M, a->N, a->N, kStoreCols, kStageRows)) return r;
+  ARG(a->act == 0 || a->act == 1, "bad act %d", a->act);
+  ARG(!a->act || (pair && a->N % 256 == 0), "act needs the CTA-pair kernel and N %% 256 == 0 (N=%d)", a->N);
+  const int ncols = a->act ? a->N / 2 : a->N;      // act: silu(gate) * up, 128 output columns per 256-column tile
+  if (int r = make_tmap(&p.tmD[0], a->Y, a->M, ncols, ncols, kStoreCols, kStageRows)) return r;
+  p.act = a->act;
   p.status = a->status; p.stamps = a->trace;
   p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
   // raster 2: n fastest (panel by panel); 3: groups of `swizzle` tile rows, n-major inside a group (wide outputs: keeps a
@@ -587,6 +595,17 @@ int ctapp_add_rmsnorm(const void* a, const void* resid, const void* gamma, void*
   GUARD(device);
   add_rmsnorm_kernel<<<M, 256, n1 * 2, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(resid), static_cast<const uint4*>(gamma),
                                                                            static_cast<uint4*>(x_out), static_cast<uint4*>(y_out), n1, eps);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+int ctapp_silu_mul(const void* in, void* out, int M, int I, int device, void* stream) {
+  ARG(in && out && M > 0 && I > 0 && I % 8 == 0, "bad arguments (M=%d I=%d)", M, I);
+  ARG(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0, "buffers must be 16-byte aligned");
+  GUARD(device);
+  const long long total = static_cast<long long>(M) * (I / 8);
+  const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), M, I);
   CU_OK(cudaGetLastError());
   return 0;
 }

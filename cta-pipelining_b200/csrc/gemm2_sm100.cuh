@@ -30,6 +30,10 @@ struct Gemm2Cfg {
   static constexpr uint32_t kTmemCols = 2 * BN;
 };
 
+// kAct: the tile's columns 0-127 are "gate" and 128-255 the matching "up" columns (the weight rows are interleaved that way
+// by the caller); the epilogue writes silu(gate) * up, 128 output columns per tile, into a D of N / 2 columns.  Both factors
+// are rounded to bf16 first, as a separate activation kernel reading the GEMM's bf16 output would see them.
+template <bool kAct>
 __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = Gemm2Cfg;
   constexpr int S = Cfg::kStages, BN = Cfg::BN;
@@ -273,13 +277,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
       const CUtensorMap* tmD = &p.tmD[dst];
 
       const uint32_t tcol = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + a * BN;
+      constexpr int kChunks = kAct ? BN / (2 * kStoreCols) : BN / kStoreCols;   // 64 output columns per chunk
 #pragma unroll 1
-      for (int c = 0; c < BN / kStoreCols; c++) {
+      for (int c = 0; c < kChunks; c++) {
         uint32_t v[2][32];
+        uint32_t u[kAct ? 2 : 1][kAct ? 32 : 1];
         tc_ld_32x32b_x32(tcol + c * kStoreCols, v[0]);
         tc_ld_32x32b_x32(tcol + c * kStoreCols + 32, v[1]);
+        if constexpr (kAct) {
+          tc_ld_32x32b_x32(tcol + BN / 2 + c * kStoreCols, u[0]);
+          tc_ld_32x32b_x32(tcol + BN / 2 + c * kStoreCols + 32, u[1]);
+        }
         tc_wait_ld();
-        if (c == BN / kStoreCols - 1) {   // accumulator fully read: hand it back to the pair's MMA thread
+        if (c == kChunks - 1) {   // accumulator fully read: hand it back to the pair's MMA thread
           tc_fence_before();
           __syncwarp();
           if (lane == 0) { if (leader) mbar_arrive_cluster_local(tempty + a); else mbar_arrive_remote(mapa_u32(tempty + a, 0)); }
@@ -289,15 +299,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         cbuf++;
         if (lane == 0) bulk_wait_read<1>();
         __syncwarp();
+        auto val = [&](int h, int i) -> float {
+          const float g = __uint_as_float(v[h][i]) * scale;
+          if constexpr (kAct) {
+            const float gb = bf16_round(g), ub = bf16_round(__uint_as_float(u[h][i]) * scale);
+            return gb / (1.0f + __expf(-gb)) * ub;
+          } else {
+            return g;
+          }
+        };
 #pragma unroll
         for (int h = 0; h < 2; h++) {
 #pragma unroll
           for (int q = 0; q < 4; q++) {
             uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[h][8 * q + 0]) * scale, __uint_as_float(v[h][8 * q + 1]) * scale);
-            o.y = pack_bf16x2(__uint_as_float(v[h][8 * q + 2]) * scale, __uint_as_float(v[h][8 * q + 3]) * scale);
-            o.z = pack_bf16x2(__uint_as_float(v[h][8 * q + 4]) * scale, __uint_as_float(v[h][8 * q + 5]) * scale);
-            o.w = pack_bf16x2(__uint_as_float(v[h][8 * q + 6]) * scale, __uint_as_float(v[h][8 * q + 7]) * scale);
+            o.x = pack_bf16x2(val(h, 8 * q + 0), val(h, 8 * q + 1));
+            o.y = pack_bf16x2(val(h, 8 * q + 2), val(h, 8 * q + 3));
+            o.z = pack_bf16x2(val(h, 8 * q + 4), val(h, 8 * q + 5));
+            o.w = pack_bf16x2(val(h, 8 * q + 6), val(h, 8 * q + 7));
             const int chunk = h * 4 + q;
             *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = o;
           }
@@ -305,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         fence_proxy_async_shared();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(tmD, buf, n * BN + c * kStoreCols, drow + lane_base);
+          tma_store_2d(tmD, buf, n * (kAct ? BN / 2 : BN) + c * kStoreCols, drow + lane_base);
           bulk_commit();
         }
       }

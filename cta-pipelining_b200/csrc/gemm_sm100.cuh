@@ -64,6 +64,7 @@ struct alignas(64) GemmParams {
   // launch behaviour
   int pdl_trigger;                 // raise the programmatic-launch trigger right after the prologue
   int pdl_wait;                    // wait for the preceding grid's memory before touching global memory
+  int act;                         // CTA-pair kernel only: 1 = silu(gate) * up epilogue over interleaved 128-column halves
   int* status;
   unsigned long long* stamps;      // 8 u64 per CTA or null
   long long limit_ns;

@@ -93,7 +93,7 @@ class TpQkvArgs(C.Structure):
     _fields_ = [("X", C.c_void_p), ("W", C.c_void_p), ("Y", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
                 ("raster", C.c_int), ("swizzle", C.c_int), ("mode", C.c_int), ("epoch", C.c_int), ("epoch_dev", C.c_void_p),
                 ("panel_flag", C.c_void_p), ("rowss", C.c_void_p), ("eps", C.c_float), ("sms", C.c_int), ("pdl", C.c_int),
-                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p), ("cta_pair", C.c_int)]
+                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p), ("cta_pair", C.c_int), ("act", C.c_int)]
 
 
 class TpReduceArgs(C.Structure):
@@ -142,6 +142,7 @@ _SIGS = {
     "ctapp_mm_order_stress": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                         C.c_void_p, C.c_int, C.c_void_p]),
     "ctapp_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "ctapp_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "ctapp_kernel_info": (C.c_int, [C.c_int, C.c_char_p, C.c_int]),
 }
 EXPORTS = tuple(_SIGS)
@@ -357,7 +358,9 @@ class Tp4Module:
         _check(self.lib.ctapp_tp_down(C.byref(a), dev, _stream(dev)))
 
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
-                tile=256, trace=0, status=None, eps=1e-5, cta_pair=0, **unsupported):
+                tile=256, trace=0, status=None, eps=1e-5, cta_pair=0, act=0, **unsupported):
+        """``act=1``: W is (2 I, K) with gate and up rows interleaved in blocks of 128 (``interleave_gate_up``) and Y is (M, I) =
+        silu(gate) * up; needs ``cta_pair``."""
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
         if mode not in (0, 5):
             raise RuntimeError(f"tp4_qkv: mode {mode} is not available in this build (0 | 5)")
@@ -365,8 +368,9 @@ class Tp4Module:
         a.X, a.W, a.Y = _ptr(X), _ptr(W), _ptr(Y)
         a.M, a.K = X.shape
         a.N = W.shape[0]
-        if W.shape[1] != a.K or tuple(Y.shape) != (a.M, a.N):
-            raise RuntimeError(f"shape mismatch X{tuple(X.shape)} W{tuple(W.shape)} Y{tuple(Y.shape)}")
+        if W.shape[1] != a.K or tuple(Y.shape) != (a.M, a.N // 2 if act else a.N):
+            raise RuntimeError(f"shape mismatch X{tuple(X.shape)} W{tuple(W.shape)} Y{tuple(Y.shape)} act={act}")
+        a.act = int(act)
         a.raster, a.swizzle, a.mode, a.epoch, a.epoch_dev = int(raster), int(swizzle), int(mode), int(epoch), _ptr(epoch_dev)
         a.panel_flag = _ptr(panel_cnt) if mode == 5 else None
         a.rowss = _ptr(rowss)
@@ -442,6 +446,18 @@ class Tp4Module:
     def tp4_step(self, epoch_dev, rowss_local, panel_done, M, role_ctr=None):
         dev = epoch_dev.device.index
         _check(self.lib.ctapp_tp_step(_ptr(epoch_dev), _ptr(rowss_local), _ptr(panel_done), int(M), _ptr(role_ctr), dev, _stream(dev)))
+
+    def silu_mul(self, g, out=None):
+        """out (M, I) = silu(g[:, :I]) * g[:, I:] for a contiguous bf16 (M, 2 I) tensor, one pass."""
+        g = _bf16_matrix(g, "g")
+        M, I2 = g.shape
+        if out is None:
+            out = torch.empty(M, I2 // 2, dtype=torch.bfloat16, device=g.device)
+        if I2 % 16 or tuple(out.shape) != (M, I2 // 2) or not out.is_contiguous():
+            raise RuntimeError(f"silu_mul: bad shapes g{tuple(g.shape)} out{tuple(out.shape)}")
+        dev = g.device.index
+        _check(self.lib.ctapp_silu_mul(_ptr(g), _ptr(out), M, I2 // 2, dev, _stream(dev)))
+        return out
 
     def add_rmsnorm(self, a, resid, gamma, x_out, y_out, eps=1e-5):
         M, n1 = a.shape

@@ -58,6 +58,16 @@ def fold_gamma(Wq, gamma):
     return (Wq.float() * gamma.float()[None, :]).to(DTYPE).contiguous()
 
 
+def interleave_gate_up(W, block=128):
+    """(2 I, K) weight with the gate rows first and the up rows second -> the same rows in blocks of ``block``: gate rows
+    0..block-1, up rows 0..block-1, gate rows block..2 block-1, ...  A 256-column output tile of the consumer GEMM then
+    holds 128 gate columns and their 128 up columns, which is what its activation epilogue (``act``) combines."""
+    two_i, K = W.shape
+    I = two_i // 2
+    assert two_i % 2 == 0 and I % block == 0, (W.shape, block)
+    return torch.stack((W[:I].view(I // block, block, K), W[I:].view(I // block, block, K)), dim=1).reshape(two_i, K).contiguous()
+
+
 # --------------------------------------------------------------------------- CTA-pipelined boundary
 class CtappBoundary:
     """CTA-pipelined boundary, panel-ownership protocol with unicast value flags (the reference's protocol "v5",
@@ -80,6 +90,8 @@ class CtappBoundary:
                      single GPU plays every rank).
     use_graph: forwards are captured into CUDA graphs keyed by (parity, M); inputs are copied into static buffers
     before each replay (``graph_bind`` captures the caller's tensors instead).
+    act: the consumer's weight is a gate/up projection with rows interleaved by ``interleave_gate_up``; its epilogue applies
+    silu(gate) * up and ``out`` is (M, N2r / 2): the activation costs no pass over memory of its own.
     cta_pair: both GEMMs run as CTA pairs (``cta_group::2``, 256-row tiles; the protocol's unit stays the 128-row panel);
     False = one CTA per 128-row tile.
     ``group_name``: a torch.distributed group name (one process per GPU) or a ``ctapp.symm.LocalGroup`` (one process
@@ -89,8 +101,10 @@ class CtappBoundary:
     def __init__(self, M, Kr, N2r, rank, world, group_name, device, resid=True, protocol="v5", use_graph=False, R=None,
                  qkv_raster=2, qkv_swizzle=1, max_M=None, down_raster=None, red_threads=1024, red_blocks=None, red_variant=1,
                  fusion="none", qkv_tile=256, role_rows=4, down_swizzle=1, pdl_trigger=None, trace=None, role_stages=0, steal=False,
-                 down_tail="auto", graph_bind=False, n1=N1, eps=EPS, cta_pair=True):
+                 down_tail="auto", graph_bind=False, n1=N1, eps=EPS, cta_pair=True, act=False):
         assert M % 128 == 0 and n1 % 256 == 0, (M, n1)
+        assert not act or (cta_pair and qkv_tile == 256 and N2r % 256 == 0), "act needs the CTA-pair consumer and N2r % 256 == 0"
+        self.act = int(bool(act))
         assert protocol in (True, False, "v3", "v5"), protocol
         assert world in (1, 2, 4, 8), f"world {world} is not supported"
         # True / "v3": NVLS variant -- the owner reducer pushes x, row sums and panel flags with multimem stores on multicast
@@ -160,7 +174,7 @@ class CtappBoundary:
             self.s_red = torch.cuda.Stream(device=dev)
             self.ev_start, self.ev_red = torch.cuda.Event(), torch.cuda.Event()
             torch.cuda.synchronize(dev)
-            self._out_full = torch.empty(max_M, N2r, dtype=DTYPE, device=dev)
+            self._out_full = torch.empty(max_M, N2r // 2 if self.act else N2r, dtype=DTYPE, device=dev)
             self._floor_y = None
             self.h_static = torch.empty(max_M, Kr, dtype=DTYPE, device=dev) if use_graph and not graph_bind else None
             self.resid_static = torch.empty(max_M, n1, dtype=DTYPE, device=dev) if use_graph and resid and not graph_bind else None
@@ -202,7 +216,7 @@ class CtappBoundary:
     def _qkv_v5(self, Wq, M, parity):
         self.ext.tp4_qkv(self.xbufs[parity][:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 5, 0, self.panel_flag, 1,
                          self.rowss[parity], sms=self.qkv_sms, pdl=1 if self.fusion == "pdl" else 0, epoch_dev=self.epoch_dev,
-                         tile=self.qkv_tile, trace=self._tr(self.trace_qkv), status=self.status, eps=self.eps, cta_pair=self.cta_pair)
+                         tile=self.qkv_tile, trace=self._tr(self.trace_qkv), status=self.status, eps=self.eps, cta_pair=self.cta_pair, act=self.act)
 
     def _enqueue_v5(self, h_r, resid, parity, Wd, Wq, M):
         cur = torch.cuda.current_stream(self.dev)
@@ -228,7 +242,7 @@ class CtappBoundary:
         self.ext.tp4_down(h_r, Wd, self._floor_y[:M], self.down_raster, self.down_swizzle, 0, self.rank, self.world, 0, sms=self.sms,
                           tail_cols=self._tail(M), cta_pair=self.cta_pair)
         self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile,
-                         cta_pair=self.cta_pair)
+                         cta_pair=self.cta_pair, act=self.act)
 
     # ---- public API
     def warmup(self):

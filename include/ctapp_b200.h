@@ -135,6 +135,11 @@ typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 
   unsigned long long* trace;
   int* status;
   int cta_pair;                            /* as in ctapp_tp_down_args; needs tile 256 */
+  int act;                                 /* 1: W holds gate and up rows interleaved in blocks of 128 (tile n = gate rows
+                                              128n.. then up rows 128n..) and Y (M, N/2) receives silu(gate) * up, both
+                                              factors rounded to bf16 first; needs cta_pair.  The reference runs the
+                                              activation as a separate kernel (vllm_plugin/ctapp_vllm/model.py:183) and
+                                              lists this fusion as future work (PLAN.md:597).  0 = off. */
 } ctapp_tp_qkv_args;
 int ctapp_tp_qkv(const ctapp_tp_qkv_args* args, int device, void* stream);
 
@@ -201,7 +206,14 @@ int ctapp_mm_order_stress(void* data_mc, const void* data_local, int* flag_mc, c
 int ctapp_add_rmsnorm(const void* a, const void* resid, const void* gamma, void* x_out, void* y_out, int M, int n1,
                       float eps, int device, void* stream);
 
-/* registers / shared memory / spill of a kernel: which = 0 GEMM 128x256, 1 GEMM 128x128, 2 reducer.  gemm_tp4.cu:374-390 */
+/* out (M, I) = silu(in[:, :I]) * in[:, I:] for in (M, 2 I) bf16, I % 8 == 0: the activation between the gate/up and the
+ * down projection as one pass, for callers that do not fuse it into ctapp_tp_qkv (act = 1) and for the comparison
+ * baselines.  No counterpart in the reference, which calls the serving stack's own kernel
+ * (vllm_plugin/ctapp_vllm/model.py:183). */
+int ctapp_silu_mul(const void* in, void* out, int M, int I, int device, void* stream);
+
+/* registers / shared memory / spill of a kernel: which = 0 GEMM 128x256, 1 GEMM 128x128, 2 reducer, 3 CTA-pair GEMM,
+ * 4 CTA-pair GEMM with the activation epilogue.  gemm_tp4.cu:374-390 */
 int ctapp_kernel_info(int which, char* buf, int buf_len);
 
 #ifdef __cplusplus

@@ -174,3 +174,14 @@ def boundary_device_model(h_full, Wdown_full, resid, gamma, Wqkv_full, world, ep
         Wf = fold_gamma(Wqkv_full, gamma)
         out = ((x.float() @ Wf.float().t()) * scale).to(torch.bfloat16)
         return x, out
+
+
+def silu_and_mul(g):
+    """(M, 2 I) bf16 -> (M, I) bf16: silu(g[:, :I]) * g[:, I:], computed in fp32 on the bf16 inputs and rounded once: the
+    activation between the gate/up and the down projection, which the reference leaves to the serving stack
+    (vllm_plugin/ctapp_vllm/model.py:183, ``mlp.act_fn``) and names as a candidate for fusion into the GEMM epilogue
+    (PLAN.md:597).  Restated from the published definition silu(x) = x / (1 + exp(-x))."""
+    import torch
+    I = g.shape[1] // 2
+    a, b = g[:, :I].float(), g[:, I:].float()
+    return (a / (1.0 + torch.exp(-a)) * b).to(torch.bfloat16)

@@ -205,3 +205,68 @@ def test_boundary_pool_one_instance_serves_every_supported_M():
         assert out.shape == (M, N2_) and bd.x().shape == (M, n1)
         assert _ulp_frac(bd.x().cpu(), x_model) >= 0.99 and _ulp_frac(out.cpu(), out_model) >= 0.98, (i, M)
     assert len(seen) == 1 and len(pool._inst) == 1
+
+
+def test_silu_mul_kernel_vs_oracle():
+    from ctapp.ext import load_tp4
+    ext = load_tp4()
+    g = (torch.randn(300, 2000, generator=torch.Generator().manual_seed(3)) * 2).to(torch.bfloat16)
+    out = ext.silu_mul(g.cuda())
+    torch.cuda.synchronize()
+    ref = ob.silu_and_mul(g)
+    d = (out.cpu().view(torch.int16).int() - ref.view(torch.int16).int()).abs()
+    assert int(d.max()) <= 1 and (d == 0).float().mean().item() >= 0.995, (int(d.max()), (d == 0).float().mean().item())
+
+
+@pytest.mark.parametrize("M,K,I", [(512, 1024, 512), (384, 512, 1280), (4096, 1024, 1792)])
+def test_consumer_gemm_activation_epilogue(M, K, I):
+    """silu(gate) * up fused into the consumer GEMM's epilogue (weight rows interleaved in blocks of 128) against the same
+    kernel without the fusion followed by the oracle's activation (at most one bf16 ulp apart: same accumulators, same
+    rounding before the activation) and against the fp32 reference within the boundary's tolerance."""
+    from ctapp.ext import load_tp4
+    from ctapp.tp4 import interleave_gate_up
+    ext = load_tp4()
+    g = torch.Generator().manual_seed(11)
+    X = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    W = (torch.randn(2 * I, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16)        # rows: gate, then up
+    rowss = (torch.rand(M, generator=g) + 0.5) * K
+    Wi = interleave_gate_up(W)
+    assert torch.equal(Wi[:128], W[:128]) and torch.equal(Wi[128:256], W[I:I + 128]) and torch.equal(Wi[256:384], W[128:256])
+    Xd, Wd_, Wid, rs = X.cuda(), W.cuda(), Wi.cuda(), rowss.cuda()
+    plain = torch.empty(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+    fused = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ext.tp4_qkv(Xd, Wd_, plain, 2, 1, 0, 0, rowss=rs, cta_pair=1)
+    ext.tp4_qkv(Xd, Wid, fused, 2, 1, 0, 0, rowss=rs, cta_pair=1, act=1)
+    torch.cuda.synchronize()
+    want = ob.silu_and_mul(plain.cpu())
+    d = (fused.cpu().view(torch.int16).int() - want.view(torch.int16).int()).abs()
+    assert int(d.max()) <= 1 and (d == 0).float().mean().item() >= 0.99, (int(d.max()), (d == 0).float().mean().item())
+    out32 = (X.float() @ W.float().t()) * torch.rsqrt(rowss / K + 1e-5)[:, None]
+    ref = ob.silu_and_mul(out32.to(torch.bfloat16))
+    mx, mean = oc.error_stats(fused.cpu(), ref)
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+    with pytest.raises(RuntimeError):
+        ext.tp4_qkv(Xd, Wid, fused, 2, 1, 0, 0, rowss=rs, cta_pair=0, act=1)          # the one-CTA kernel has no such epilogue
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_boundary_with_activation_epilogue(world):
+    """The whole boundary with a gate/up consumer: every rank's out is silu(gate_r) * up_r of the oracle's model output."""
+    from ctapp.tp4 import forward_lockstep, interleave_gate_up
+    M, K, n1, N2_ = 512, 1024, 2048, 2048
+    bds = _setup(world, [0] * world, M, K, n1, N2_, act=True)
+    Kr, N2r = K // world, N2_ // world
+    Wd, gamma, Wq = ob.make_weights(seed=5, K=K, N2_=N2_, n1=n1)
+    h, resid = ob.make_inputs(M, seed=105, K=K, n1=n1)
+    sh = [ob.shard_weights(Wd, Wq, gamma, r, world) for r in range(world)]
+    outs = forward_lockstep(bds, [h[:, r * Kr:(r + 1) * Kr].contiguous().cuda() for r in range(world)], [resid.cuda()] * world,
+                            [sh[r][0].cuda() for r in range(world)], [interleave_gate_up(sh[r][2]).cuda() for r in range(world)])
+    for bd in bds:
+        bd.check()
+    _, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, world)
+    for r in range(world):
+        assert tuple(outs[r].shape) == (M, N2r // 2)
+        want = ob.silu_and_mul(out_model[:, r * N2r:(r + 1) * N2r].contiguous())
+        mx, mean = oc.error_stats(outs[r].cpu(), want)
+        assert mx <= 2e-2 and mean <= 1e-3, (r, mx, mean)
+        assert _ulp_frac(outs[r].cpu(), want) >= 0.97, _ulp_frac(outs[r].cpu(), want)

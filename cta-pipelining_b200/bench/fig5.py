@@ -55,7 +55,7 @@ def main():
             tp = mt.TensorParallel2(M, X, W1a, W2b)
             r["tp2_cublas_nccl_us"] = measure(tp, a.reps)[0]
         bestc = None
-        for gr in [v if v == "ramp" else int(v) for v in a.groups.split(",")]:
+        for gr in [v if v in ("ramp", "head") else int(v) for v in a.groups.split(",")]:
             c = mt.Ctapp(M, X, W1a, W2b, a.cfg, a.cfg, gr)
             t = measure(c, a.reps)[0]
             c.pl.check()

@@ -70,10 +70,35 @@ def ramp_groups(tm, peak=8):
     return head + sizes + tail[::-1]
 
 
+def head_groups(tm, peak=8):
+    """Group sizes 1, 1, 2, 4, ..., then ``peak`` for the rest of ``tm`` tile rows: the first row panels complete after one
+    wave (a short fill for the next stage), everything after the ramp keeps the L2 reuse of large groups.  For chains whose
+    steps overlap, where what is left at the end of a step never idles the next stage."""
+    sizes, g, left = [], 1, tm
+    for a in (1, 1):
+        if left > 0:
+            sizes.append(a); left -= a
+    g = 2
+    while left > 0:
+        a = min(g, peak, left)
+        sizes.append(a); left -= a
+        g *= 2
+    return sizes
+
+
+def _group_sizes(group_rows, tm):
+    """List of group sizes for the named or listed variable-group orders."""
+    if group_rows == "ramp":
+        return ramp_groups(tm)
+    if group_rows == "head":
+        return head_groups(tm)
+    return list(group_rows)
+
+
 def producer_order(P, tn1, group_rows):
     """Tile ids in the order the first stage works through them: groups of tile rows, n-major inside a group (reference
     ctapp/pipeline.py:48-51 for a constant group size).  ``group_rows``: 0 = ascending ids; an int = constant group size;
-    "ramp" or a list of group sizes = variable groups (``ramp_groups``)."""
+    "ramp" (``ramp_groups``), "head" (``head_groups``) or a list of group sizes = variable groups."""
     if not group_rows:
         return torch.arange(P, dtype=torch.int32)
     tm = P // tn1
@@ -81,7 +106,7 @@ def producer_order(P, tn1, group_rows):
         t = torch.arange(P)
         m, n = t // tn1, t % tn1
         return torch.argsort(((m // group_rows) * tn1 + n) * group_rows + m % group_rows, stable=True).int()
-    sizes = ramp_groups(tm) if group_rows == "ramp" else list(group_rows)
+    sizes = _group_sizes(group_rows, tm)
     assert sum(sizes) == tm and all(s > 0 for s in sizes), (sizes, tm)
     out, m0 = [], 0
     for g in sizes:
@@ -126,7 +151,7 @@ def consumer_window(group_rows, rowpanel, bm_prev, bm, tm=0):
         return g if g > 1 else 0
     if bm_prev != bm:
         return 0
-    return ramp_groups(tm) if group_rows == "ramp" else list(group_rows)
+    return _group_sizes(group_rows, tm)
 
 
 def _window_args(win, dev):

@@ -248,6 +248,6 @@ def test_chain_stages_one_process_per_gpu_overlapped_steps(cfg):
     import mp_cases
     from ctapp.tp4 import launch
     world = 4 if torch.cuda.device_count() >= 4 else 2
-    res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg, 2 if cfg == 3 else "ramp")
+    res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg, 2 if cfg == 3 else "head")
     assert not bad, res
     assert all(r == [] for r in res), res

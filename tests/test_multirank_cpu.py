@@ -40,6 +40,27 @@ def _shards_cover(rank, world, dev, group_name, seed):
     return rank
 
 
+def _orders_and_windows_agree(rank, world, dev, group_name, tm, tn, group_rows):
+    """Rank 0 computes the order it works in, every later rank the windows it pops its queue in: when the producer publishes
+    its row panels group by group, the consuming rank's tile order is the producer's own, all the way down the chain; and the
+    set the ranks use for step e of a link with doubled buffers is the same on both sides."""
+    import torch
+    import torch.distributed as dist
+    from ctapp.pipeline import consumer_window, pop_slots, producer_order
+    n = tm * tn
+    mine = producer_order(n, tn, group_rows) if rank == 0 else None
+    win = 0 if rank == 0 else consumer_window(group_rows, 1, 256, 256, tm)
+    got = [None] * world
+    dist.all_gather_object(got, (mine, win, [(e, e & 1) for e in range(1, 6)]))
+    order0 = got[0][0]
+    if rank > 0:
+        slots = pop_slots(n, tn, win if win else 1)
+        # the producer finishes its groups in order, so panel p sits in queue slots [p * tn, (p + 1) * tn) as tile ids p * tn + j
+        assert torch.equal(slots, order0), (rank, group_rows)
+    assert all(g[2] == got[0][2] for g in got)
+    return rank
+
+
 def _one_rank_raises(rank, world, dev, group_name):
     if rank == 1:
         raise RuntimeError("injected failure on rank 1")
@@ -58,6 +79,13 @@ def test_stage_plans_agree_over_gloo():
     res, bad = launch(_plans_agree, 2, 29631, 1024, 512, [768, 1024], backend="gloo")
     assert not bad, res
     assert [r["ntiles"] for r in res] == [8 * 3, 8 * 4] and res[0]["deps"] == 24
+
+
+def test_producer_order_and_consumer_windows_agree_over_gloo():
+    from ctapp.tp4 import launch
+    for port, (tm, tn, gr) in enumerate([(32, 32, "head"), (16, 8, 8), (9, 4, "ramp"), (12, 4, [3, 4, 5])]):
+        res, bad = launch(_orders_and_windows_agree, 2, 29640 + port, tm, tn, gr, backend="gloo")
+        assert not bad and res == [0, 1], (res, tm, tn, gr)
 
 
 def test_weight_shards_cover_over_gloo():

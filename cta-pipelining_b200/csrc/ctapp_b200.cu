@@ -311,6 +311,29 @@ int ctapp_config_info(int config_id, char* buf, int buf_len) {
 }
 int ctapp_occupancy(int config_id) { return cfg_bn(config_id) ? 1 : fail(-1, "bad config_id %d", config_id); }
 
+int ctapp_cluster_occupancy(int cluster_size, int device) {
+  if (cluster_size < 1 || cluster_size > 16) return fail(-1, "bad cluster size %d", cluster_size);
+  DeviceGuard g_(device);
+  if (!g_.ok) return fail(-2, "cannot select device %d", device);
+  cudaError_t e = cudaFuncSetAttribute(gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes);
+  if (e == cudaSuccess && cluster_size > 8) e = cudaFuncSetAttribute(gemm2_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return fail(-static_cast<int>(e) - 100, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(sm_count(device) / cluster_size * cluster_size);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Gemm2Cfg::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, gemm2_kernel<false>, &cfg);
+  if (e != cudaSuccess) return fail(-static_cast<int>(e) - 100, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));
+  return n;
+}
+
 int ctapp_kernel_info(int which, char* buf, int buf_len) {
   ARG(buf && buf_len > 0, "null buffer");
   cudaFuncAttributes a;

@@ -127,6 +127,7 @@ _SIGS = {
     "ctapp_ipc_close": (C.c_int, [C.c_void_p, C.c_int]),
     "ctapp_config_info": (C.c_int, [C.c_int, C.c_char_p, C.c_int]),
     "ctapp_occupancy": (C.c_int, [C.c_int]),
+    "ctapp_cluster_occupancy": (C.c_int, [C.c_int, C.c_int]),
     "ctapp_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "ctapp_chain_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(ChainArgs), C.c_int, C.c_void_p]),
     "ctapp_chain_reset": (C.c_int, [Queue, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
@@ -274,6 +275,13 @@ class ChainModule:
         buf = C.create_string_buffer(256)
         _check(self.lib.ctapp_config_info(int(config_id), buf, 256))
         return buf.value.decode()
+
+    def cluster_occupancy(self, cluster_size, device=0):
+        """Clusters of ``cluster_size`` CTAs of the CTA-pair kernel the device holds at once."""
+        n = self.lib.ctapp_cluster_occupancy(int(cluster_size), int(device))
+        if n < 0:
+            raise RuntimeError(f"ctapp_cluster_occupancy: {self.lib.ctapp_last_error().decode()}")
+        return n
 
     def occupancy(self, config_id):
         n = self.lib.ctapp_occupancy(int(config_id))

@@ -54,6 +54,10 @@ int ctapp_ipc_close(void* ptr, int device);
  * the reference) is the CTA-pair kernel: a cluster of two CTAs, cta_group::2, protocol tile 256 x 256 x 64. */
 int ctapp_config_info(int config_id, char* buf, int buf_len);   /* text contains "tile BMxBNxBK" */
 int ctapp_occupancy(int config_id);                              /* resident CTAs per SM */
+/* How many clusters of `cluster_size` CTAs of the CTA-pair kernel (its threads and shared memory) the device can hold at
+ * once (cudaOccupancyMaxActiveClusters); negative = error.  A cluster lives inside one GPC, so sizes that do not divide a
+ * GPC's SM count leave SMs idle: the figure that decides whether a wider cluster can pay.  No counterpart in the reference. */
+int ctapp_cluster_occupancy(int cluster_size, int device);
 
 /* Y[M,N] = X[M,K] * W[N,K]^T, bf16 in, fp32 accumulate, bf16 out.  gemm_tma.cu:128-134 (gemm_tma), gemm_coop.cu:101-114
  * (coop_gemm).  group_rows: tile rows walked together (0 = library default); sms: CTAs to launch (0 = all SMs). */

@@ -101,3 +101,17 @@ def test_gemm_rejects_bad_arguments():
         ext.gemm_tma(X, W[:, :32].contiguous(), Y, 3)
     with pytest.raises(RuntimeError):
         ext.gemm_tma(X[:, :36].contiguous(), W[:, :36].contiguous(), Y, 3)   # K not a multiple of 8
+
+
+def test_cluster_occupancy_probe():
+    """CTA pairs fill the device; wider clusters can hold at most as many SMs."""
+    from ctapp.ext import load
+    ext = load()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pairs = ext.cluster_occupancy(2)
+    assert pairs == sms // 2, (pairs, sms)
+    for c in (4, 8):
+        n = ext.cluster_occupancy(c)
+        assert 1 <= n <= sms // c, (c, n)
+    with pytest.raises(RuntimeError):
+        ext.cluster_occupancy(0)

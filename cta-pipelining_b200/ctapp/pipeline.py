@@ -71,14 +71,11 @@ def ramp_groups(tm, peak=8):
 
 
 def head_groups(tm, peak=8):
-    """Group sizes 1, 1, 2, 4, ..., then ``peak`` for the rest of ``tm`` tile rows: the first row panels complete after one
-    wave (a short fill for the next stage), everything after the ramp keeps the L2 reuse of large groups.  For chains whose
-    steps overlap, where what is left at the end of a step never idles the next stage."""
-    sizes, g, left = [], 1, tm
-    for a in (1, 1):
-        if left > 0:
-            sizes.append(a); left -= a
-    g = 2
+    """Group sizes 2, 4, ..., then ``peak`` for the rest of ``tm`` tile rows.  The first wave of a GEMM covers a little more than
+    two tile rows whatever the order, so a first group of two completes as early as anything can (a short fill for the next
+    stage), and everything after the ramp keeps the L2 reuse of large groups.  For chains whose steps overlap, where what
+    is left at the end of a step never idles the next stage."""
+    sizes, g, left = [], 2, tm
     while left > 0:
         a = min(g, peak, left)
         sizes.append(a); left -= a

@@ -30,7 +30,7 @@ def test_ramped_and_listed_producer_orders():
         g = ramp_groups(tm)
         assert sum(g) == tm and all(1 <= v <= 8 for v in g) and g[0] == 1 and g[-1] == 1
     from ctapp.pipeline import head_groups
-    assert head_groups(32) == [1, 1, 2, 4, 8, 8, 8] and head_groups(1) == [1] and head_groups(3) == [1, 1, 1] and head_groups(11) == [1, 1, 2, 4, 3]
+    assert head_groups(32) == [2, 4, 8, 8, 8, 2] and head_groups(1) == [1] and head_groups(3) == [2, 1] and head_groups(11) == [2, 4, 5]
     assert sorted(producer_order(11 * 4, 4, "head").tolist()) == list(range(44))
     o = producer_order(32 * 32, 32, "ramp")
     assert sorted(o.tolist()) == list(range(1024))

@@ -137,7 +137,8 @@ def run_reference(args, rank):
 def workload_config(args, n):
     return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
                         + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
-            "M": args.m, "N": NK, "K": NK, "stages": n, "tile": "256x256x64 per CTA pair (cta_group::2)", "parallelism": f"pp{n}",
+            "M": args.m, "N": NK, "K": NK, "stages": n, "tile": {10: "256x256x64 per CTA pair (cta_group::2)", 11: "256x512x64 per CTA pair (cta_group::2, one TMEM accumulator)",
+                                                                       3: "128x256x64 per CTA"}[args.cfg], "parallelism": f"pp{n}",
             "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)",
             "steps_overlap": "none (one GEMM per step)" if n == 1 else
             "consecutive steps stream through the stages like batches through a layer pipeline: every link (buffer, queue, "
@@ -347,6 +348,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cfg", type=int, default=GEMM_CFG, choices=[3, 10, 11],
+                    help="chain: GEMM configuration id (10 = CTA pair on 256x256x64 tiles, 11 = CTA pair on 256x512x64, 3 = one CTA on 128x256x64)")
     ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
@@ -422,12 +425,12 @@ def main():
     gr = (8 if world <= 2 else "head") if gr == "auto" else (gr if gr in ("ramp", "head") else int(gr))
     args.group_rows = gr
     if world == 1:
-        chain = Chain(M, NK, [NK], [local_rank], cfg=GEMM_CFG, group_rows=args.group_rows)
+        chain = Chain(M, NK, [NK], [local_rank], cfg=args.cfg, group_rows=args.group_rows)
         step = lambda: chain.run(X_dev, [Wmine])  # noqa: E731
         checker = chain.check
         launches_per_step = 2   # reset kernel + GEMM kernel
     else:
-        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=GEMM_CFG, group_rows=args.group_rows)
+        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=args.cfg, group_rows=args.group_rows)
         step = lambda: stage.step(Wmine, X_dev)  # noqa: E731
         checker = stage.check
         launches_per_step = 2 * n

@@ -100,15 +100,17 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long lon
 // ------------------------------------------------------------------------------------------ configurations
 // Reference ids 0-9 name wgmma tiles (64|128 x 128|256).  A 64-row UMMA tile has no place here (one CTA drives a
 // 128-lane TMEM accumulator), so every id resolves to the 128-row tile with the same width.
-// Ids 10 and up are this library's own: 10 = CTA pair (cta_group::2) working on a 256 x 256 tile.
+// Ids 10 and up are this library's own: 10 = CTA pair (cta_group::2) working on a 256 x 256 tile, 11 = CTA pair on a
+// 256 x 512 tile (single TMEM accumulator).
 static int cfg_bn(int id) {
   switch (id) {
     case 0: case 1: case 5: case 7: return 128;
     case 2: case 3: case 4: case 6: case 8: case 9: case 10: return 256;
+    case 11: return 512;
     default: return 0;
   }
 }
-static bool cfg_pair(int id) { return id == 10; }
+static bool cfg_pair(int id) { return id == 10 || id == 11; }
 static int sm_count(int dev) {
   static std::atomic<int> cache[64];
   if (dev < 0 || dev >= 64) return 0;
@@ -153,29 +155,32 @@ static int fill_common(GemmParams& p, const void* A, const void* B, int M, int N
   ARG(A && B, "null operand");
   ARG(M > 0 && N > 0 && K > 0, "bad shape M=%d N=%d K=%d", M, N, K);
   ARG(K % 8 == 0 && N % 8 == 0, "K=%d and N=%d must be multiples of 8", K, N);
-  ARG(!pair || bn == 256, "the CTA-pair kernel has 256-column tiles");
+  ARG(!pair || bn == 256 || bn == 512, "the CTA-pair kernel has 256- or 512-column tiles");
   p.M = M; p.N = N; p.K = K;
   p.panels = (M + BM - 1) / BM;
   p.tiles_m = pair ? (M + 2 * BM - 1) / (2 * BM) : p.panels;
   p.tiles_n = (N + bn - 1) / bn;
   p.num_tiles = p.tiles_m * p.tiles_n;
   if (int r = make_tmap(&p.tmA, A, M, K, K, BK, BM)) return r;
-  if (int r = make_tmap(&p.tmB, B, N, K, K, BK, pair ? bn / 2 : bn)) return r;
+  if (int r = make_tmap(&p.tmB, B, N, K, K, BK, pair ? 128 : bn)) return r;   // pair: each CTA loads 128 weight rows per MMA
   return 0;
 }
 
-static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t stream) {
+static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t stream, bool wide = false) {
   const int nsm = sm_count(dev);
   int pairs = (sms > 0 && sms < nsm ? sms : nsm) / 2;
   if (pairs > p.num_tiles) pairs = p.num_tiles;
   if (pairs < 1) return 0;
   p.limit_ns = limit_ns();
-  CU_OK(cudaFuncSetAttribute(p.act ? gemm2_kernel<true> : gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  if (wide && p.act) return fail(-1, "the 256 x 512 tile has no activation epilogue");
+  const unsigned smem = wide ? Gemm2CfgT<true>::kSmemBytes : Gemm2Cfg::kSmemBytes;
+  CU_OK(cudaFuncSetAttribute(wide ? gemm2_kernel<false, true> : p.act ? gemm2_kernel<true> : gemm2_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Gemm2Cfg::kSmemBytes;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
@@ -189,7 +194,8 @@ static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t s
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (p.act) CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<true>, p));
+  if (wide) CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<false, true>, p));
+  else if (p.act) CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<true>, p));
   else CU_OK(cudaLaunchKernelEx(&cfg, gemm2_kernel<false>, p));
   return 0;
 }
@@ -300,8 +306,9 @@ int ctapp_config_info(int config_id, char* buf, int buf_len) {
   const int bn = cfg_bn(config_id);
   ARG(bn && buf && buf_len > 0, "bad config_id %d", config_id);
   if (cfg_pair(config_id)) {
-    snprintf(buf, buf_len, "tcgen05 cta_group::2 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=%d cluster=2", 2 * BM, bn, BK,
-             kThreads, Gemm2Cfg::kSmemBytes, Gemm2Cfg::kStages, 2 * bn);
+    const bool wide = bn == 512;
+    snprintf(buf, buf_len, "tcgen05 cta_group::2 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=512 cluster=2", 2 * BM, bn, BK,
+             kThreads, wide ? Gemm2CfgT<true>::kSmemBytes : Gemm2Cfg::kSmemBytes, wide ? Gemm2CfgT<true>::kStages : Gemm2Cfg::kStages);
     return 0;
   }
   const int stages = bn == 256 ? GemmCfg<256>::kStages : GemmCfg<128>::kStages;
@@ -337,7 +344,7 @@ int ctapp_cluster_occupancy(int cluster_size, int device) {
 int ctapp_kernel_info(int which, char* buf, int buf_len) {
   ARG(buf && buf_len > 0, "null buffer");
   cudaFuncAttributes a;
-  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel<false> : which == 4 ? (const void*)gemm2_kernel<true> : (const void*)tp_reduce_kernel<4, 2>;
+  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel<false> : which == 4 ? (const void*)gemm2_kernel<true> : which == 5 ? (const void*)gemm2_kernel<false, true> : (const void*)tp_reduce_kernel<4, 2>;
   CU_OK(cudaFuncGetAttributes(&a, fn));
   snprintf(buf, buf_len, "regs=%d local=%zu static_smem=%zu max_threads=%d", a.numRegs, a.localSizeBytes, a.sharedSizeBytes, a.maxThreadsPerBlock);
   return 0;
@@ -356,6 +363,7 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false>));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<true>));
+  CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false, true>));
   CU_OK(cudaFuncGetAttributes(&a, silu_mul_kernel));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<1, false>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, false>));
@@ -368,6 +376,7 @@ int ctapp_preload(int device) {
   if (int r = prepare_kernel<128>()) return r;
   CU_OK(cudaFuncSetAttribute(gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
   CU_OK(cudaFuncSetAttribute(gemm2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
+  CU_OK(cudaFuncSetAttribute(gemm2_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2CfgT<true>::kSmemBytes));
   return 0;
 }
 
@@ -384,7 +393,7 @@ int ctapp_gemm(const void* X, const void* W, void* Y, int M, int N, int K, int c
   p.mode = kModePlain;
   p.order = kOrderGrouped;
   p.group_rows = group_rows > 0 ? group_rows : (pair ? 8 : 16);
-  if (pair) return launch_gemm2(p, sms, 0, device, static_cast<cudaStream_t>(stream));
+  if (pair) return launch_gemm2(p, sms, 0, device, static_cast<cudaStream_t>(stream), bn == 512);
   return launch_gemm(p, bn, sms, 0, device, static_cast<cudaStream_t>(stream));
 }
 
@@ -417,7 +426,7 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   p.src_windows = a->src_windows; p.n_windows = a->src_windows ? a->n_windows : 0;
   p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
   p.status = a->status; p.stamps = a->stamps;
-  if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream));
+  if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream), bn == 512);
   return launch_gemm(p, bn, a->sms, 0, device, static_cast<cudaStream_t>(stream));
 }
 

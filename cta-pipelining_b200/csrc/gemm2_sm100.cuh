@@ -18,24 +18,31 @@
 
 namespace ctapp {
 
-struct Gemm2Cfg {
-  static constexpr int BN = 256;
-  static constexpr int kStages = 6;
+// kWide: the pair's tile is 256 x 512 (two 256-column MMAs per k step that share the A operand in shared memory): 48 KiB of
+// operands per CTA and k-block for twice the work, a quarter less traffic L2 -> shared memory per FLOP than the 256 x 256
+// tile.  The price: the accumulator takes all 512 TMEM columns, so the epilogue of a tile no longer overlaps the main loop
+// of the next one, and tiles are twice as coarse.
+template <bool kWide> struct Gemm2CfgT {
+  static constexpr int BN = kWide ? 512 : 256;
+  static constexpr int kStages = kWide ? 4 : 6;               // 192 KiB of operands in flight either way
+  static constexpr int kAccs = kWide ? 1 : 2;                 // TMEM accumulators
   static constexpr uint32_t kABytes = BM * BK * 2;            // this CTA's 128 rows of A
   static constexpr uint32_t kBBytes = (BN / 2) * BK * 2;      // this CTA's half of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;  // per CTA
   static constexpr uint32_t kEpiBytes = 4 * 2 * kStageRows * kStoreCols * 2;
   static constexpr uint32_t kBarBytes = 512;
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
-  static constexpr uint32_t kTmemCols = 2 * BN;
+  static constexpr uint32_t kTmemCols = 512;
 };
+using Gemm2Cfg = Gemm2CfgT<false>;
 
 // kAct: the tile's columns 0-127 are "gate" and 128-255 the matching "up" columns (the weight rows are interleaved that way
 // by the caller); the epilogue writes silu(gate) * up, 128 output columns per tile, into a D of N / 2 columns.  Both factors
 // are rounded to bf16 first, as a separate activation kernel reading the GEMM's bf16 output would see them.
-template <bool kAct>
+template <bool kAct, bool kWide = false>
 __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = Gemm2Cfg;
+  static_assert(!(kAct && kWide), "the activation epilogue is built for the 256-column tile");
+  using Cfg = Gemm2CfgT<kWide>;
   constexpr int S = Cfg::kStages, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -158,7 +165,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           if (!mbar_wait(empty + stage, phase ^ 1, s_abort, limit)) { ok = false; break; }
           if (leader) mbar_arrive_expect_tx(full + stage, 2 * Cfg::kStageBytes);   // both CTAs' bytes are counted here
           tma_load_2d_pair(sA + stage * Cfg::kABytes, &p.tmA, kb * BK, m * BM, full0 + stage * 8);
-          tma_load_2d_pair(sB + stage * Cfg::kBBytes, &p.tmB, kb * BK, n * BN + static_cast<int>(crank) * (BN / 2), full0 + stage * 8);
+          if constexpr (kWide) {   // accumulator columns 0-255 and 256-511: each CTA supplies 128 weight rows of either half
+            tma_load_2d_pair(sB + stage * Cfg::kBBytes, &p.tmB, kb * BK, n * BN + static_cast<int>(crank) * 128, full0 + stage * 8);
+            tma_load_2d_pair(sB + stage * Cfg::kBBytes + Cfg::kBBytes / 2, &p.tmB, kb * BK, n * BN + 256 + static_cast<int>(crank) * 128, full0 + stage * 8);
+          } else {
+            tma_load_2d_pair(sB + stage * Cfg::kBBytes, &p.tmB, kb * BK, n * BN + static_cast<int>(crank) * (BN / 2), full0 + stage * 8);
+          }
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == S) { stage = 0; phase ^= 1; }
@@ -185,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
   } else if (warp == 1) {
     // ============================================================ MMA issuer (leader only)
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, 256);
       int stage = 0; uint32_t phase = 0; int sq = 0; uint32_t sphase = 0; uint32_t it = 0;
       bool ok = true;
       while (ok) {
@@ -194,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         mbar_arrive_cluster_local(sempty + sq);
         if (++sq == kSchedSlots) { sq = 0; sphase ^= 1; }
         if (tile < 0) break;
-        const uint32_t a = it & 1u, aphase = (it >> 1) & 1u;
+        const uint32_t a = kWide ? 0u : (it & 1u), aphase = kWide ? (it & 1u) : ((it >> 1) & 1u);
         if (!mbar_wait_cluster(tempty + a, aphase ^ 1, s_abort, limit)) break;
         tc_fence_after();
         const uint32_t d = tmem_base + a * BN;
@@ -203,9 +215,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           tc_fence_after();
           const uint64_t adesc = umma_desc_k128(sA + stage * Cfg::kABytes);
           const uint64_t bdesc = umma_desc_k128(sB + stage * Cfg::kBBytes);
+          const uint64_t bdesc2 = umma_desc_k128(sB + stage * Cfg::kBBytes + Cfg::kBBytes / 2);   // wide tile: each CTA's other 128 weight rows
 #pragma unroll
-          for (int k = 0; k < BK / 16; k++)
+          for (int k = 0; k < BK / 16; k++) {
             tc_mma_f16_pair(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (kWide) tc_mma_f16_pair(d + 256, adesc + 2 * k, bdesc2 + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);   // same A
+          }
           tc_commit_pair(empty + stage, 3);   // frees the stage in both CTAs
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
@@ -245,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
       if (p.mode == kModeChain) { mp = tile / p.tiles_n; n = tile - mp * p.tiles_n; } else decode_tile(p, tile, mp, n);
       const int m = 2 * mp + static_cast<int>(crank);
       const bool valid = m < p.panels;            // an odd panel count leaves the last pair's second half empty
-      const uint32_t a = it & 1u, aphase = (it >> 1) & 1u;
+      const uint32_t a = kWide ? 0u : (it & 1u), aphase = kWide ? (it & 1u) : ((it >> 1) & 1u);
       it++;
       if (!warp_wait(tfull + a, aphase)) break;
       tc_fence_after();

@@ -51,7 +51,9 @@ int ctapp_ipc_close(void* ptr, int device);
 
 /* ---- GEMM configurations (csrc/gemm_tma.cu:116-126, 155-165) ----
  * ids 0-9 are the reference's; each resolves to a one-CTA tcgen05 tile 128 x {128|256} x 64.  id 10 (no counterpart in
- * the reference) is the CTA-pair kernel: a cluster of two CTAs, cta_group::2, protocol tile 256 x 256 x 64. */
+ * the reference) is the CTA-pair kernel: a cluster of two CTAs, cta_group::2, protocol tile 256 x 256 x 64; id 11 is the
+ * same kernel on a 256 x 512 x 64 tile (a quarter less operand traffic per FLOP, one TMEM accumulator: for large plain or
+ * chained GEMMs; the tensor-parallel entry points keep the 256-column tile). */
 int ctapp_config_info(int config_id, char* buf, int buf_len);   /* text contains "tile BMxBNxBK" */
 int ctapp_occupancy(int config_id);                              /* resident CTAs per SM */
 /* How many clusters of `cluster_size` CTAs of the CTA-pair kernel (its threads and shared memory) the device can hold at

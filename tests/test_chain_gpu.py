@@ -43,6 +43,7 @@ def _run_case(M, K, N1, N2, cfg1, cfg2, devA, devB, runs=3, **kw):
 @pytest.mark.parametrize("case", [(256, 512, 512, 768, 3, 3, {}), (512, 1024, 1024, 1024, 5, 3, dict(group_rows=2)),
                                   (512, 512, 1024, 768, 10, 10, {}), (768, 512, 768, 1024, 10, 3, dict(group_rows=2)), (640, 256, 512, 512, 3, 10, dict(scoreboard="tile")),
                                   (384, 512, 512, 512, 10, 10, dict(group_rows=1)),
+                                  (768, 512, 1024, 1536, 11, 11, dict(group_rows=2)), (512, 256, 1280, 768, 10, 11, {}), (1024, 512, 1024, 512, 11, 3, dict(group_rows="head")),
                                   (2048, 512, 512, 768, 3, 3, dict(group_rows="ramp")), (2304, 256, 768, 512, 10, 10, dict(group_rows=[1, 3, 4, 1])),
                                   (384, 512, 768, 512, 3, 5, dict(scoreboard="tile")), (1000, 520, 1000, 264, 5, 5, dict(group_rows=8))])
 def test_chain_one_gpu_small(case):

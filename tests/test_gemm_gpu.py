@@ -38,7 +38,7 @@ def _check(Y, ref_f32, what):
     assert ulp_ok >= 0.999, f"{what}: only {ulp_ok:.5f} of the elements within one bf16 ulp of the oracle"
 
 
-@pytest.mark.parametrize("cfg", [3, 5, 10])
+@pytest.mark.parametrize("cfg", [3, 5, 10, 11])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 512), (200, 264, 72),
                                    (1000, 520, 1000), (2048, 2048, 2048)])
 def test_gemm_small_shapes(cfg, shape):
@@ -58,14 +58,14 @@ def test_gemm_chain_config_vs_oracle():
     X, Ws = oc.make_chain_inputs(M, K, [N], seed=0)
     Y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     ref = X.float() @ Ws[0].float().t()
-    for cfg in (3, 10):
+    for cfg in (3, 10, 11):
         Y.fill_(float("nan"))
         ext.gemm_tma(X.cuda(), Ws[0].cuda(), Y, cfg)
         torch.cuda.synchronize()
         _check(Y.cpu(), ref, f"chain stage 1024x8192x8192 cfg {cfg}")
 
 
-@pytest.mark.parametrize("cfg", [3, 5, 10])
+@pytest.mark.parametrize("cfg", [3, 5, 10, 11])
 def test_gemm_full_size_properties(cfg):
     """At the benchmark's full size the CPU oracle is too slow; use size-independent properties instead:
     (1) exact linearity in a power-of-two scale of the input, (2) identical results for any CTA count / tile order,

@@ -34,7 +34,7 @@ import torch  # noqa: E402
 
 NK = 8192
 GEMM_CFG = 10        # CTA-pair tcgen05 kernel, 256 x 256 x 64 tiles (two TMEM accumulators)
-GEMM_CFG_1GPU = 11   # the same kernel on 256 x 512 x 64 tiles (one TMEM accumulator, a quarter less operand traffic)
+GEMM_CFG_WIDE = 11   # the same kernel on 256 x 512 x 64 tiles (one TMEM accumulator, a quarter less operand traffic)
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
                "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 # DRAM traffic of one 8192^3 GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture summarised
@@ -137,7 +137,7 @@ def run_reference(args, rank):
 
 def workload_config(args, n):
     if args.cfg == "auto":
-        args.cfg = GEMM_CFG_1GPU if n == 1 else GEMM_CFG
+        args.cfg = GEMM_CFG_WIDE if n <= 2 else GEMM_CFG
     args.cfg = int(args.cfg)
     return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
                         + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
@@ -354,7 +354,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cfg", default="auto", choices=["auto", "3", "10", "11"],
                     help="chain: GEMM configuration id (10 = CTA pair on 256x256x64 tiles, 11 = CTA pair on 256x512x64, 3 = one CTA on "
-                    "128x256x64; auto = 11 on one GPU, where it measured 5.5 %% faster, and 10 on several, where the wider tile has not been timed)")
+                    "128x256x64; auto = 11 on one and two GPUs, where it measured 5.5 %% and 2-6 %% faster, and 10 from three on, where the wider tile has not been timed)")
     ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
@@ -426,7 +426,7 @@ def main():
     X_dev = X_host.to(dev) if rank == 0 else None
     Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
 
-    args.cfg = (GEMM_CFG_1GPU if world == 1 else GEMM_CFG) if args.cfg == "auto" else int(args.cfg)
+    args.cfg = (GEMM_CFG_WIDE if world <= 2 else GEMM_CFG) if args.cfg == "auto" else int(args.cfg)
     gr = args.group_rows
     gr = (8 if world <= 2 else "head") if gr == "auto" else (gr if gr in ("ramp", "head") else int(gr))
     args.group_rows = gr

@@ -136,3 +136,40 @@ def test_integer_artefacts_equal_the_oracle_on_random_shapes():
             w = consumer_window(g, 1, BM1, BM2, tm2)
             slots = pop_slots(tm2 * tn2, tn2, w if w else 1).numpy()
             assert sorted(slots.tolist()) == list(range(tm2 * tn2))
+
+
+def test_doubled_links_schedule_has_no_cycle_and_no_set_reuse():
+    """Model of ``ChainStage``'s schedule for L ranks and E steps.  Kernels of a rank run in stream order: step e enqueues the
+    reset that prepares the link set of step e+1 (and raises its ready flag upstream), then the GEMM of step e.  A GEMM cannot
+    finish before its producer's GEMM of the same step has, and a producer cannot store step e before the consumer's reset for
+    step e.  The dependency graph must be acyclic (nothing can wait for itself), and a link set (e & 1) must never be reset
+    for step e+2 while the GEMM that reads step e from it can still be running."""
+    from graphlib import TopologicalSorter
+    L, E = 4, 7
+    deps = {}
+
+    def add(node, *before):
+        deps.setdefault(node, set()).update(before)
+
+    for g in range(L):
+        prev = None
+        stream = [("reset", g, 1)] + [op for e in range(1, E + 1) for op in (("reset", g, e + 1), ("gemm", g, e))]
+        for op in stream:                                  # stream order on rank g
+            add(op, *([prev] if prev else []))
+            prev = op
+        for e in range(1, E + 1):
+            if g > 0:
+                add(("gemm", g, e), ("gemm", g - 1, e))      # all of the producer's tiles of step e
+                add(("gemm", g - 1, e), ("reset", g, e))     # the producer's first store of step e waits for this rank's ready flag
+    order = list(TopologicalSorter(deps).static_order())    # raises CycleError on a deadlock
+    pos = {op: i for i, op in enumerate(order)}
+    for g in range(1, L):
+        for e in range(1, E - 1):
+            # the set of step e is prepared again for step e+2 only after this rank's GEMM of step e ...
+            assert ("gemm", g, e) in deps[("reset", g, e + 2)] or pos[("gemm", g, e)] < pos[("reset", g, e + 2)]
+            stream = [op for op in order if op[1] == g]
+            assert stream.index(("gemm", g, e)) < stream.index(("reset", g, e + 2))
+            # ... and the producer's step e+2, which writes that set, cannot start storing before that reset
+            assert ("reset", g, e + 2) in deps[("gemm", g - 1, e + 2)]
+    # at most two steps of a link are in flight: the producer's step e+2 needs the consumer's step e to be over
+    assert all(pos[("gemm", g, e)] < pos[("gemm", g - 1, e + 2)] for g in range(1, L) for e in range(1, E - 1))

@@ -294,7 +294,7 @@ template <int W> static int launch_reduce_tma(const ReduceParams& p, const void*
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 1; }
+int ctapp_abi_version(void) { return 2; }   // 2: src_group / src_windows / n_windows in ctapp_chain_args, act in ctapp_tp_qkv_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;

@@ -24,6 +24,7 @@ SOURCES = ["ctapp_b200.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", "reduce_tma_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+ABI_VERSION = 2
 STATUS_INTS = 8
 MAX_WORLD = 8
 
@@ -160,6 +161,8 @@ def lib():
         for name, (res, args) in _SIGS.items():
             fn = getattr(l, name)
             fn.restype, fn.argtypes = res, args
+        if l.ctapp_abi_version() != ABI_VERSION:     # the ctypes structs below must match the library's argument structs
+            raise RuntimeError(f"{path} has ABI version {l.ctapp_abi_version()}, these bindings need {ABI_VERSION}: rebuild it")
         _lib = l
     return _lib
 

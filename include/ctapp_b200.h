@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 2 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);

@@ -56,3 +56,18 @@ def test_python_module_surface():
     assert "tile 128x256x64" in m1.config_info(3)
     with pytest.raises(RuntimeError):
         m1.config_info(99)
+
+
+def test_build_entry_point_runs():
+    """``__graft_entry__.build()`` is what decides "does it build": it must compile the library in-tree, load it, agree with
+    the bindings on the ABI version and import the package."""
+    import importlib
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    entry = importlib.import_module("__graft_entry__")
+    entry.build()
+    from ctapp import ext
+    assert os.path.exists(ext.LIB_PATH) and ext.lib().ctapp_abi_version() == ext.ABI_VERSION

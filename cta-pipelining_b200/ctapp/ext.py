@@ -57,12 +57,16 @@ def build(force=False, verbose=False):
         if os.path.exists(LIB_PATH):
             return LIB_PATH            # cannot rebuild here; use what was shipped
         raise RuntimeError("libctapp_b200.so is not built and nvcc was not found (set CUDA_HOME)")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *[os.path.join(CSRC, s) for s in SOURCES]]
+    tmp = f"{LIB_PATH}.{os.getpid()}.tmp"     # built beside the target and renamed: a process that has the old file mapped keeps it
+    cmd = [nvcc, *NVCC_FLAGS, "-o", tmp, *[os.path.join(CSRC, s) for s in SOURCES]]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         print(" ".join(cmd)); print(r.stdout); print(r.stderr)
     if r.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError(f"nvcc failed ({r.returncode}):\n{r.stderr[-4000:]}")
+    os.replace(tmp, LIB_PATH)
     with open(os.path.join(ROOT, "build_ptxas.log"), "w") as f:
         f.write(r.stderr)
     return LIB_PATH

@@ -37,9 +37,17 @@ GEMM_CFG = 10        # CTA-pair tcgen05 kernel, 256 x 256 x 64 tiles (two TMEM a
 GEMM_CFG_WIDE = 11   # the same kernel on 256 x 512 x 64 tiles (one TMEM accumulator, a quarter less operand traffic)
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
                "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-# DRAM traffic of one 8192^3 GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture summarised
-# in profiles/gemm2_kernel_chain_stage.md; the capture is of an M=2048 launch and traffic grows in proportion to M
-GEMM_DRAM_TRAFFIC_BYTES = int(4 * 272.67e6)   # 272.67 MB measured at M=2048 (profiles/gemm2_kernel_chain_stage.md), scaled by 8192 / 2048 rows
+# measured DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum of one launch under ncu) per configuration id, captured on
+# an M = 2048 launch of the same kernel: {"<cfg>": {"M": 2048, "bytes": ...}}; traffic grows in proportion to M
+TRAFFIC_FILE = os.path.join(ROOT, "cta-pipelining_b200", "bench", "ncu_traffic.json")
+
+
+def dram_traffic(cfg, M):
+    try:
+        rec = json.load(open(TRAFFIC_FILE)).get(str(cfg))
+        return int(rec["bytes"] * M / rec["M"]) if rec else None
+    except (OSError, ValueError, KeyError):
+        return None
 
 
 def peaks():
@@ -112,7 +120,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    M_s = min(args.m, 2048)                     # bounded sample: the first M_s token rows of the workload
+    M_s = args.m                                # the whole workload: every token row through every stage, every step
     n = max(args.gpus, 1)
     ts = []
     from oracle import chain as oc
@@ -130,7 +138,7 @@ def run_reference(args, rank):
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": workload_config(args, n),
             "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                             "sample": f"first {M_s} of {args.m} token rows, all {n} stages, torch CPU fp32 F.linear chain"},
+                             "sample": f"all {M_s} token rows, all {n} stages, torch CPU fp32 F.linear chain, {args.steps} steps"},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -150,23 +158,29 @@ def workload_config(args, n):
             "in flight per link; ms_per_step is the K steps' total time / K, fill included"}
 
 
-def run_boundary(args, rank, world, local_rank):
+def _init_groups(world, dev, port):
+    """NCCL default group + gloo side group for the stand-alone workloads (idempotent)."""
+    import torch.distributed as dist
+    from ctapp import tp4
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if not dist.is_initialized():
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", str(port))
+            dist.init_process_group("gloo", rank=0, world_size=1)
+    if tp4.GLOO is None:
+        tp4.GLOO = dist.new_group(backend="gloo")
+
+
+def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     """TP layer boundary at TP = world: down-proj partial GEMM (K = 28672 / t, N = 8192, M tokens) -> cross-rank sum + bf16
     residual + RMSNorm (eps 1e-5) -> QKV GEMM (K = 8192, N = 10240 / t).  Times the CTA-pipelined boundary, its two-GEMM floor,
     and the stock boundary (cuBLAS GEMM + NCCL all-reduce + one fused add+RMSNorm kernel + cuBLAS GEMM); back-to-back mean and
-    per-step median, max over ranks.  One JSON line on rank 0."""
+    per-step median, max over ranks.  Process groups must be up.  Returns the record (rank 0) or None."""
     import torch.distributed as dist
     from ctapp import tp4
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    else:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29577")
-        dist.init_process_group("gloo", rank=0, world_size=1)
-    tp4.GLOO = dist.new_group(backend="gloo")
-    M = args.m
+    M = M or args.m
     t = world
     Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
     kfull = Kr * t
@@ -181,16 +195,19 @@ def run_boundary(args, rank, world, local_rank):
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
     iters, warm = max(args.steps, 10), max(args.warmup, 3)
     res = {}
-    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw, **(dict(red_variant=args.red_variant) if args.red_variant else {}))
+    steal = bool(args.steal) if args.steal in (0, 1) else t >= 4
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion,
+                           R=None if args.R < 0 else args.R, steal=steal, **akw)
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
-    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=args.R or None, **akw)
+    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=bd.R if bd.R else None, **akw)
     res["two_gemm_floor"] = tp4.time_step(lambda: fl.forward(h_r, None, Wd_r, Wqf_r), dev, iters, warm)
     st = tp4.NcclFusedNormBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
     res["cublas_nccl_fusednorm"] = tp4.time_step(lambda: st.forward(h_r, resid), dev, iters, warm)
-    st2 = tp4.NcclBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
-    res["cublas_nccl_eagernorm"] = tp4.time_step(lambda: st2.forward(h_r, resid), dev, iters, warm)
+    if with_eager:
+        st2 = tp4.NcclBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
+        res["cublas_nccl_eagernorm"] = tp4.time_step(lambda: st2.forward(h_r, resid), dev, iters, warm)
     unavailable = {}
     if args.baselines == "strong" and t > 1:
         for name, cls in (("cublas_multimem_ar_eagernorm", tp4.MultimemBoundary), ("asynctp_matmul_reduce_scatter", tp4.AsyncTpBoundary)):
@@ -209,15 +226,63 @@ def run_boundary(args, rank, world, local_rank):
     torch.cuda.synchronize(dev)
     rel = float((o1 - o2).abs().max() / o2.abs().max())
     tp4.barrier()
+    if rank != 0:
+        return None
+    flops = 2 * M * Kr * tp4.N1 + 2 * M * tp4.N1 * N2r
+    burst, sustained, kind = peaks()
+    b2b = res["ctapp"][1]
+    return {"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
+            "n_gpus": t, "fusion": args.fusion, "steal": steal, "R": bd.R, "push": "nvls multimem" if bd.nvls else "unicast",
+            "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
+            "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
+            "over_two_gemm_floor_b2b": b2b / res["two_gemm_floor"][1],
+            "tflops_per_gpu_b2b": flops / (b2b * 1e-3) / 1e12, "frac_of_burst_peak": flops / (b2b * 1e-3) / 1e12 / burst,
+            "out_rel_vs_stock": rel, "iters": iters, "unavailable": unavailable}
+
+
+def run_boundary(args, rank, world, local_rank):
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    _init_groups(world, dev, 29577)
+    rec = boundary_record(args, rank, world, dev)
     if rank == 0:
-        flops = 2 * M * Kr * tp4.N1 + 2 * M * tp4.N1 * N2r
-        burst, sustained, kind = peaks()
-        b2b = res["ctapp"][1]
-        print(json.dumps({"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
-                          "n_gpus": t, "fusion": args.fusion, "R": bd.R, "push": "nvls multimem" if bd.nvls else "unicast", "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
-                          "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
-                          "tflops_per_gpu_b2b": flops / (b2b * 1e-3) / 1e12, "frac_of_burst_peak": flops / (b2b * 1e-3) / 1e12 / burst,
-                          "out_rel_vs_stock": rel, "iters": iters, "unavailable": unavailable}), flush=True)
+        print(json.dumps(rec), flush=True)
+
+
+def latency_record(M_list, cfg, reps=10):
+    """Gated single-run latency of the two-stage chain on GPUs 0 and 1, driven from this one process (the other ranks idle at a
+    barrier): the north-star figure, chain time over the ideal = one library GEMM's time (both layers on one GPU / 2), beside
+    micro-batched library GEMMs with peer copies.  Mirrors reference bench/fig5.py:29-93 for the M given."""
+    from ctapp import methods as mt
+    from ctapp.timing import measure
+    g = torch.Generator().manual_seed(0)
+    W1 = (torch.randn(NK, NK, generator=g) / NK ** 0.5).to(torch.bfloat16)
+    W2 = (torch.randn(NK, NK, generator=g) / NK ** 0.5).to(torch.bfloat16)
+    W1a, W2a, W2b = W1.to(mt.dev(0)), W2.to(mt.dev(0)), W2.to(mt.dev(1))
+    rows = []
+    for M in M_list:
+        X = torch.randn(M, NK, generator=g).to(torch.bfloat16).to(mt.dev(0))
+        r = {"M": M}
+        r["ideal_us"] = measure(mt.OneGpuCublas(M, X, W1a, W2a), reps, devs=(0,))[0] / 2
+        r["ours_one_gpu_half_us"] = measure(mt.OneGpuTma(M, X, W1a, W2a, cfg), reps, devs=(0,))[0] / 2
+        best = None
+        for chunk in (512, 1024):
+            t = measure(mt.MicroBatchCublas(M, X, W1a, W2b, chunk), reps)[0]
+            best = (t, chunk) if best is None or t < best[0] else best
+        r["microbatch_cublas_us"], r["microbatch_chunk"] = best
+        for name, kw in (("rowpanel_g2", dict(group_rows=2)), ("kchunk_g4", dict(group_rows=4, scoreboard="kchunk")),
+                         ("kchunk_g8", dict(group_rows=8, scoreboard="kchunk"))):
+            c = mt.Ctapp(M, X, W1a, W2b, cfg, cfg, kw["group_rows"], scoreboard=kw.get("scoreboard", "rowpanel"))
+            r[f"chain_{name}_us"] = measure(c, reps)[0]
+            c.pl.check()
+            del c
+        r["chain_us"] = min(v for k, v in r.items() if k.startswith("chain_"))
+        r["over_ideal"] = r["chain_us"] / r["ideal_us"]
+        r["vs_microbatch"] = r["microbatch_cublas_us"] / r["chain_us"]
+        rows.append({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})
+        del X
+        torch.cuda.empty_cache()
+    return rows
 
 
 def run_reducer(args, rank, world, local_rank):
@@ -228,18 +293,12 @@ def run_reducer(args, rank, world, local_rank):
     from ctapp import tp4
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    else:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29579")
-        dist.init_process_group("gloo", rank=0, world_size=1)
-    tp4.GLOO = dist.new_group(backend="gloo")
+    _init_groups(world, dev, 29579)
     M, t = args.m, world
     out = {}
-    rv = dict(red_variant=args.red_variant) if args.red_variant else {}
+    rv = {}
     resid = torch.randn(M, tp4.N1, device=dev).to(torch.bfloat16)
-    for R in ([args.R] if args.R else [4, 8, 16, 32]):
+    for R in ([args.R] if args.R > 0 else [4, 8, 16, 32]):
         bd = tp4.CtappBoundary(M, 256, 256, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, R=R, **rv)
         bd.inbox.normal_()
         ext = bd.ext
@@ -250,7 +309,7 @@ def run_reducer(args, rank, world, local_rank):
             bd.tile_flags.fill_(bd.epoch)                      # every producer tile "has arrived"
             torch.cuda.synchronize(dev); tp4.barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); bd._reduce_v5(M, resid, bd.epoch & 1); b.record()
+            a.record(); bd.launch_reducer(M, resid, bd.epoch & 1); b.record()
             torch.cuda.synchronize(dev); tp4.barrier()
             if it >= max(args.warmup, 3):
                 times.append(a.elapsed_time(b))
@@ -269,7 +328,7 @@ def run_reducer(args, rank, world, local_rank):
             link = (t - 1) * S / (ms * 1e-3) / 1e9
             rows[R] = {"ms": round(ms, 4), "hbm_GBs": round(hbm, 1), "hbm_frac_of_measured_peak": round(hbm / peak_hbm, 4),
                        "nvlink_egress_GBs": round(link, 1), "nvlink_frac_of_770": round(link / 770.0, 4)}
-        print(json.dumps({"workload": f"owner reducer alone (variant {args.red_variant or 'default'}), TP{t}, M={M}, n1=8192, push={'nvls' if args.protocol == 'v3' and t > 1 else 'unicast'}",
+        print(json.dumps({"workload": f"owner reducer alone, TP{t}, M={M}, n1=8192, push={'nvls' if args.protocol == 'v3' and t > 1 else 'unicast'}",
                           "bytes_per_rank": {"hbm_read": (t + 1) * S, "hbm_write": t * S, "nvlink_egress": (t - 1) * S}, "by_R": rows}), flush=True)
     tp4.barrier()
 
@@ -283,13 +342,7 @@ def run_stages(args, rank, world, local_rank):
     from ctapp import tp4
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    else:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29580")
-        dist.init_process_group("gloo", rank=0, world_size=1)
-    tp4.GLOO = dist.new_group(backend="gloo")
+    _init_groups(world, dev, 29580)
     M, t = args.m, world
     Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
     akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4, down_tail=tp4.N1 // 256)
@@ -298,7 +351,7 @@ def run_stages(args, rank, world, local_rank):
     Wq = (torch.randn(N2r, tp4.N1, generator=g) * tp4.N1 ** -0.5).to(torch.bfloat16).to(dev)
     h = torch.randn(M, Kr, generator=g).to(torch.bfloat16).to(dev)
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
-    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=args.R or None, **akw)
+    bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion, R=None if args.R < 0 else args.R, **akw)
     ext, iters = bd.ext, max(args.steps, 10)
     y0 = torch.empty(M, tp4.N1, dtype=torch.bfloat16, device=dev)
 
@@ -326,12 +379,12 @@ def run_stages(args, rank, world, local_rank):
         ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, M, bd.role_ctr)
 
     res = {}
-    res["producer_mode0_local"] = b2b(lambda: ext.tp4_down(h, Wd, y0, 1, 1, 0, rank, t, 0, sms=bd.sms, tail_cols=bd._tail(M), cta_pair=bd.cta_pair))
-    res["producer_mode7_scatter"] = b2b(lambda: bd._down_v5(h, Wd, M), step)
-    res["reducer_alone"] = b2b(lambda: bd._reduce_v5(M, resid, bd.epoch & 1))            # flags of the last scatter are still up
+    res["producer_mode0_local"] = b2b(lambda: ext.tp4_down(h, Wd, y0, 1, 1, 0, rank, t, 0, sms=bd.sms, tail_cols=bd.tail_cols(M), cta_pair=bd.cta_pair))
+    res["producer_mode7_scatter"] = b2b(lambda: bd.launch_producer(h, Wd, M), step)
+    res["reducer_alone"] = b2b(lambda: bd.launch_reducer(M, resid, bd.epoch & 1))            # flags of the last scatter are still up
     res["consumer_mode0"] = b2b(lambda: ext.tp4_qkv(bd.xbufs[bd.epoch & 1][:M], Wq, bd._out_full[:M], bd.qkv_raster, bd.qkv_swizzle, 0, 0, sms=bd.qkv_sms,
                                                    tile=bd.qkv_tile, cta_pair=bd.cta_pair))
-    res["consumer_mode5_flags_up"] = b2b(lambda: bd._qkv_v5(Wq, M, bd.epoch & 1))
+    res["consumer_mode5_flags_up"] = b2b(lambda: bd.launch_consumer(Wq, M, bd.epoch & 1))
     res["boundary"] = b2b(lambda: bd.forward(h, resid, Wd, Wq))
     bd.check()
     if rank == 0:
@@ -362,13 +415,16 @@ def main():
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8 up to two GPUs, 'head' from "
                     "three: steps overlap, so the fill is paid once per run and per link; on 2 GPUs 'head' measured 0.7-0.9 %% slower than 8)")
-    ap.add_argument("--fusion", default="pdl", choices=["none", "pdl"])
+    ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
+    ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = on from TP4")
+    ap.add_argument("--no-sustained", action="store_true", help="chain: keep the one-second sustained loop as short as the timed region (profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="chain: skip the gated-latency, boundary and oracle records that follow the timed regions")
     ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
     ap.add_argument("--baselines", default="stock", choices=["stock", "strong"],
                     help="boundary: strong = also torch's multimem all-reduce and async-TP (fused matmul + reduce-scatter) boundaries")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
-    ap.add_argument("--red-variant", type=int, default=0, help="boundary / reducer: 1 = warp-per-unit reducer, 3 = TMA-fed reducer, 0 = library default")
-    ap.add_argument("--R", type=int, default=0, help="boundary: SMs reserved for the owner reducer (0 = library default: 4 up to TP2, 8 from TP4)")
+    ap.add_argument("--R", type=int, default=-1, help="boundary: SMs reserved for the owner reducer (-1 = library default: 4 up to TP2, 8 from TP4; 0 with "
+                    "--steal 1 = none, the consumer's CTAs do the reduction)")
     args = ap.parse_args()
     if args.m is None:
         args.m = 4096 if args.workload == "boundary" and args.impl == "ours" else 8192
@@ -458,10 +514,18 @@ def main():
         torch.cuda.synchronize(dev)
         barrier()
         ms_total = max_over_ranks(a.elapsed_time(b))
-        # keep the GPU busy a little longer so that the 100 ms sampler sees clocks under load (same step count on every rank)
-        for _ in range(int(min(2000, 600.0 / max(ms_total / K_steps, 0.05)))):
+        # the same steps for about a second more (same count on every rank): what the 100 ms clock sampler can see, and the
+        # sustained figure at the power cap that goes with those clocks
+        n_tail = K_steps if args.no_sustained else int(min(4000, 1000.0 / max(ms_total / K_steps, 0.05)))
+        barrier()
+        a_t, b_t = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_t.record()
+        for _ in range(n_tail):
             step()
+        b_t.record()
         torch.cuda.synchronize(dev)
+        barrier()
+        sustained_ms = max_over_ranks(a_t.elapsed_time(b_t)) / n_tail
     checker()
     ms_step = ms_total / K_steps
     value = flops_step / (ms_step * 1e-3) / 1e12
@@ -544,6 +608,53 @@ def main():
     assert stage_rel <= 2e-2, f"a stage's output differs from a library matmul of its input: {stage_rel}"
     barrier()
 
+    # ---- the last step's output against the CPU oracle: the first 256 token rows through ALL stages on the host (rows are
+    # independent, so a row sample is a complete check of those rows), max relative / mean absolute error after normalising
+    # by the output RMS, bounds 2e-2 / 1e-3
+    ROWS = 256
+    y_rows = (chain.Y[0] if world == 1 else stage.Yout)[:ROWS].cpu() if rank == n - 1 else torch.empty(ROWS, NK, dtype=torch.bfloat16)
+    if world > 1:
+        yb = y_rows.view(torch.int16)
+        dist.broadcast(yb, src=n - 1, group=gloo)
+        y_rows = yb.view(torch.bfloat16)
+    oracle_check = None
+    if rank == 0:
+        from oracle import chain as oc
+        torch.set_num_threads(os.cpu_count() or 1)
+        g2 = torch.Generator().manual_seed(0)
+        x_rows = torch.randn(M, NK, generator=g2).to(torch.bfloat16)[:ROWS]
+        assert torch.equal(x_rows, X_host[:ROWS])
+        Ws_cpu = [(torch.randn(NK, NK, generator=g2) / NK ** 0.5).to(torch.bfloat16) for _ in range(n)]
+        mx, mean = oc.error_stats(y_rows, oc.chain_reference(x_rows, Ws_cpu))
+        oracle_check = {"rows": ROWS, "stages": n, "max_rel": mx, "mean_abs": mean, "bounds": [2e-2, 1e-3], "ok": bool(mx <= 2e-2 and mean <= 1e-3)}
+        del Ws_cpu
+    barrier()
+
+    # ---- the north-star records that go with the line (untimed extras): the gated single-run latency of the two-stage chain
+    # against one library GEMM, and the tensor-parallel layer boundary against cuBLAS + NCCL + fused norm at TP = N
+    latency = boundary = None
+    if world >= 2 and not args.no_extras:
+        step = step_x = checker = stage = None       # the chain's buffers go before the extras allocate theirs
+        X_dev = xbufs = ybufs = inp = got = last_x = None
+        torch.cuda.empty_cache()
+        barrier()
+        if rank == 0:
+            try:
+                latency = latency_record([4096, 8192], GEMM_CFG)
+            except Exception as e:  # noqa: BLE001
+                latency = {"error": repr(e)[:300]}
+            torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+            torch.cuda.empty_cache()
+        barrier()
+        from ctapp import tp4
+        tp4.GLOO = gloo
+        bargs = argparse.Namespace(**{**vars(args), "shape": "B", "steps": 10, "warmup": 3, "baselines": "stock"})
+        try:
+            boundary = boundary_record(bargs, rank, world, dev, M=4096, with_eager=False)
+        except Exception as e:  # noqa: BLE001
+            boundary = {"error": repr(e)[:300]}
+        barrier()
+
     if rank != 0:
         return
     burst, sustained, kind = peaks()
@@ -552,11 +663,19 @@ def main():
             "config": workload_config(args, n), "clocks": clk.summary(),
             "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": M * NK * 2, "d2h_bytes_per_step": M * NK * 2},
-            "gpu_launches": launches_per_step * K_steps, "stage_output_check_max_rel": stage_rel}
+            "gpu_launches": launches_per_step * K_steps, "stage_output_check_max_rel": stage_rel, "oracle_check": oracle_check,
+            "sustained": {"ms_per_step": sustained_ms, "value": flops_step / (sustained_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n_tail,
+                          "note": "the same steps back to back for about a second; the clocks key was sampled over the timed region plus this loop"}}
+    if latency is not None:
+        line["latency"] = {"what": "2-stage chain on GPUs 0 and 1, one gated run (host launch cost outside the window), median; ideal = one "
+                                   "library GEMM = both layers on one GPU / 2; target over_ideal <= 1.15 at M >= 4096", "rows": latency}
+    if boundary is not None:
+        line["boundary"] = boundary
+    assert oracle_check["ok"], f"the timed configuration's output differs from the CPU oracle: {oracle_check}"
     if True:
         ach = 2 * M * NK * NK / (kernel_ms * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst,
-                            "traffic": GEMM_DRAM_TRAFFIC_BYTES if args.cfg == 10 and M == 8192 else None,   # the ncu capture is of config 10
+                            "traffic": dram_traffic(args.cfg, M),
                             "peak_kind": f"{kind} burst bf16 ({'kernel timed alone' if world == 1 else 'per GPU: one stage kernel spans the pipelined run'}, {kernel_ms:.3f} ms per launch)",
                             "frac_of_sustained": ach / sustained, "kernel": {10: "gemm2_kernel<false, false>", 11: "gemm2_kernel<false, true>", 3: "gemm_kernel<256>"}[args.cfg], "flop_per_launch": 2 * M * NK * NK}
     if not args.no_cpu_baseline and world == 1:

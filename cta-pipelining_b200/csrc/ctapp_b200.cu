@@ -15,7 +15,6 @@
 #include "gemm_sm100.cuh"
 #include "gemm2_sm100.cuh"
 #include "reduce_sm100.cuh"
-#include "reduce_tma_sm100.cuh"
 
 using namespace ctapp;
 
@@ -214,8 +213,9 @@ __global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb
 }
 
 template <int W> static int launch_reduce(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
-  if (p.x_mc) tp_reduce_kernel<W, (W > 4 ? 1 : 2), true><<<blocks, threads, 0, s>>>(p);
-  else tp_reduce_kernel<W, (W > 4 ? 1 : 2)><<<blocks, threads, 0, s>>>(p);
+  constexpr int R = RedRows<W>::value;
+  if (p.x_mc) tp_reduce_kernel<W, R, true><<<blocks, threads, 0, s>>>(p);
+  else tp_reduce_kernel<W, R><<<blocks, threads, 0, s>>>(p);
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -270,31 +270,60 @@ static int noalloc_scratch_ptr(int device, unsigned char** out) {
   return 0;
 }
 
-template <int W> static int launch_reduce_tma(const ReduceParams& p, const void* const* inbox, const void* resid, int ppo, int blocks, cudaStream_t s) {
-  using Cfg = RedTmaCfg<W>;
-  ReduceTmaParams tp;
-  memset(&tp, 0, sizeof(tp));
-  tp.r = p;
-  tp.has_resid = resid != nullptr;
-  for (int i = 0; i < W; i++)
-    if (int r = make_tmap(&tp.tmIn[i], inbox[i], static_cast<long long>(ppo) * 128, p.n1, p.n1, Cfg::kChunkCols, kRedUnitRows, false)) return r;
-  if (resid)
-    if (int r = make_tmap(&tp.tmIn[W], resid, p.M, p.n1, p.n1, Cfg::kChunkCols, kRedUnitRows, false)) return r;
-  if (p.x_mc) {
-    CU_OK(cudaFuncSetAttribute(tp_reduce_tma_kernel<W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    tp_reduce_tma_kernel<W, true><<<blocks, kRedThreads, Cfg::kSmemBytes, s>>>(tp);
-  } else {
-    CU_OK(cudaFuncSetAttribute(tp_reduce_tma_kernel<W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    tp_reduce_tma_kernel<W, false><<<blocks, kRedThreads, Cfg::kSmemBytes, s>>>(tp);
+// Checks a reducer argument block and turns it into kernel parameters.  `own_scratch`: rowss_local / panel_done come from the
+// caller (required); otherwise the caller of this function supplies them afterwards.
+static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_scratch) {
+  ARG(a, "null args");
+  ARG(a->world == 1 || a->world == 2 || a->world == 4 || a->world == 8, "world %d is not supported (1 | 2 | 4 | 8)", a->world);
+  ARG(a->rank >= 0 && a->rank < a->world, "bad rank %d", a->rank);
+  ARG(a->M >= 0 && a->M % 128 == 0 && a->n1 > 0 && a->n1 % 256 == 0, "bad shape M=%d n1=%d", a->M, a->n1);
+  ARG(a->tile_flags, "null tile_flags");
+  ARG(!own_scratch || (a->rowss_local && a->panel_done), "null rowss_local / panel_done");
+  ARG(a->tail_cols >= 0 && a->tail_cols <= a->n1 / 256, "bad tail_cols %d", a->tail_cols);
+  ARG(a->order >= 0 && a->order <= 2 && a->swz >= 0, "bad unit order %d / swz %d", a->order, a->swz);
+  // flags are indexed (source * panels_per_owner + owned panel): a smaller value than the panels this rank owns would make
+  // the sources' flags alias each other, a larger one than the allocation reads out of bounds (the caller's to guarantee)
+  ARG(a->panels_per_owner >= (a->M / 128 + a->world - 1) / a->world, "panels_per_owner %d is too small for M=%d on %d ranks (needs >= %d)",
+      a->panels_per_owner, a->M, a->world, (a->M / 128 + a->world - 1) / a->world);
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.n1 = a->n1; p.rank = a->rank; p.world = a->world;
+  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
+  p.tile_flags = a->tile_flags;
+  for (int d = 0; d < a->world; d++) {
+    ARG(a->inbox[d] && a->peer_x[d] && a->peer_rowss[d] && a->peer_panel_flag[d], "missing peer buffer %d", d);
+    p.inbox[d] = static_cast<const uint4*>(a->inbox[d]);
+    p.x[d] = static_cast<uint4*>(a->peer_x[d]);
+    p.rowss[d] = a->peer_rowss[d];
+    p.panel_flag[d] = a->peer_panel_flag[d];
   }
-  CU_OK(cudaGetLastError());
+  p.resid = static_cast<const uint4*>(a->resid);
+  p.rowss_local = a->rowss_local; p.panel_done = a->panel_done;
+  p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
+  p.order = a->order ? a->order : 1; p.swz = a->swz;
+  p.unit_ctr = a->unit_ctr; p.unit_log = a->unit_log; p.trace = a->trace; p.status = a->status;
+  p.pdl_trigger = a->pdl_trigger;
+  if (a->x_mc || a->rowss_mc || a->panel_flag_mc) {   // NVLS variant: all three multicast addresses or none
+    ARG(a->x_mc && a->rowss_mc && a->panel_flag_mc, "the NVLS variant needs x_mc, rowss_mc and panel_flag_mc");
+    ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
+    p.x_mc = static_cast<uint4*>(a->x_mc); p.rowss_mc = a->rowss_mc; p.panel_flag_mc = a->panel_flag_mc;
+  }
+  p.limit_ns = limit_ns();
   return 0;
+}
+
+static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
+  switch (p.world) {
+    case 1: return launch_reduce<1>(p, blocks, threads, s);
+    case 2: return launch_reduce<2>(p, blocks, threads, s);
+    case 4: return launch_reduce<4>(p, blocks, threads, s);
+    default: return launch_reduce<8>(p, blocks, threads, s);
+  }
 }
 
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 2; }   // 2: src_group / src_windows / n_windows in ctapp_chain_args, act in ctapp_tp_qkv_args
+int ctapp_abi_version(void) { return 3; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;
@@ -344,7 +373,7 @@ int ctapp_cluster_occupancy(int cluster_size, int device) {
 int ctapp_kernel_info(int which, char* buf, int buf_len) {
   ARG(buf && buf_len > 0, "null buffer");
   cudaFuncAttributes a;
-  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel<false> : which == 4 ? (const void*)gemm2_kernel<true> : which == 5 ? (const void*)gemm2_kernel<false, true> : (const void*)tp_reduce_kernel<4, 2>;
+  const void* fn = which == 0 ? (const void*)gemm_kernel<256> : which == 1 ? (const void*)gemm_kernel<128> : which == 3 ? (const void*)gemm2_kernel<false> : which == 4 ? (const void*)gemm2_kernel<true> : which == 5 ? (const void*)gemm2_kernel<false, true> : (const void*)tp_reduce_kernel<4, RedRows<4>::value>;
   CU_OK(cudaFuncGetAttributes(&a, fn));
   snprintf(buf, buf_len, "regs=%d local=%zu static_smem=%zu max_threads=%d", a.numRegs, a.localSizeBytes, a.sharedSizeBytes, a.maxThreadsPerBlock);
   return 0;
@@ -355,23 +384,22 @@ int ctapp_preload(int device) {
   cudaFuncAttributes a;
   CU_OK(cudaFuncGetAttributes(&a, gemm_kernel<256>));
   CU_OK(cudaFuncGetAttributes(&a, gemm_kernel<128>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<1, 2>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 2>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 2>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 1>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<1, RedRows<1>::value>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, RedRows<2>::value>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, RedRows<4>::value>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, RedRows<8>::value>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, RedRows<2>::value, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, RedRows<4>::value, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, RedRows<8>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false>));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<true>));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false, true>));
   CU_OK(cudaFuncGetAttributes(&a, silu_mul_kernel));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<1, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<4, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<8, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<2, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<4, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_tma_kernel<8, true>));
+  CU_OK(cudaFuncGetAttributes(&a, chain_reset_kernel));
+  unsigned char* scratch = nullptr;   // the allocation-free reducer's scratch address, so that its first call does no set-up either
+  if (int r = noalloc_scratch_ptr(device, &scratch)) return r;
   if (int r = prepare_kernel<256>()) return r;
   if (int r = prepare_kernel<128>()) return r;
   CU_OK(cudaFuncSetAttribute(gemm2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Cfg::kSmemBytes));
@@ -424,7 +452,13 @@ int ctapp_chain_gemm(const void* X, const void* W, void* Y, int M, int N, int K,
   p.src_group = a->src_group;
   ARG(!a->src_windows || a->n_windows > 0, "src_windows needs n_windows > 0");
   p.src_windows = a->src_windows; p.n_windows = a->src_windows ? a->n_windows : 0;
-  p.dst_ready = a->dep_offsets ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
+  p.dst_ready = (a->dep_offsets || a->chunk_dst) ? a->dst_ready : nullptr; p.ready_value = a->ready_value;
+  if (a->chunk_src) {
+    ARG(a->chunk_kblocks > 0 && a->chunk_cols > 0 && a->chunk_cols * a->chunk_kblocks * BK >= K, "k-chunk flags: %d chunks of %d k-blocks do not cover K=%d",
+        a->chunk_cols, a->chunk_kblocks, K);
+    p.chunk_src = a->chunk_src; p.chunk_kblocks = a->chunk_kblocks; p.chunk_cols = a->chunk_cols;
+  }
+  p.chunk_dst = a->chunk_dst; p.chunk_value = a->chunk_value;
   p.status = a->status; p.stamps = a->stamps;
   if (pair) return launch_gemm2(p, a->sms, 0, device, static_cast<cudaStream_t>(stream), bn == 512);
   return launch_gemm(p, bn, a->sms, 0, device, static_cast<cudaStream_t>(stream));
@@ -449,8 +483,10 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
   GemmParams p;
   if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, 256, pair)) return r;
   ARG(a->N % 256 == 0, "N=%d must be a multiple of 256", a->N);
-  p.status = a->status; p.stamps = a->trace;
-  p.pdl_trigger = a->pdl_trigger; p.pdl_wait = a->pdl;
+  p.status = a->status; p.stamps = a->trace; p.tile_log = a->tile_log;
+  // mode 7 launched as a programmatic dependent follows the owner reducer, which waits for THIS kernel's tiles: it must not
+  // wait for that grid to finish (the step kernel before the reducer has completed by then: stream order)
+  p.pdl_trigger = a->pdl_trigger; p.pdl_wait = a->mode == 7 ? 0 : a->pdl;
   p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
   if (a->raster == 2) p.order = kOrderNFast;
   else {
@@ -463,8 +499,10 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
     p.mode = kModePlain;
   } else {
     ARG(a->M % 128 == 0, "mode 7 needs M %% 128 == 0 (M=%d)", a->M);
-    ARG(a->dst_rows >= ((a->M / 128 + a->world - 1) / a->world) * 128 && a->panels_per_owner * 128 <= a->dst_rows,
-        "inbox slot of %d rows / %d panels per owner is too small for M=%d on %d ranks", a->dst_rows, a->panels_per_owner, a->M, a->world);
+    ARG(a->dst_rows >= ((a->M / 128 + a->world - 1) / a->world) * 128 && a->panels_per_owner * 128 <= a->dst_rows &&
+            a->panels_per_owner >= (a->M / 128 + a->world - 1) / a->world,
+        "inbox slot of %d rows / %d panels per owner does not fit M=%d on %d ranks (panels_per_owner must be >= ceil(M/128/world) and its rows <= dst_rows)",
+        a->dst_rows, a->panels_per_owner, a->M, a->world);
     p.mode = kModeTpProducer;
     p.world = a->world; p.rank = a->rank; p.ppo = a->panels_per_owner;
     for (int d = 0; d < a->world; d++) {
@@ -479,7 +517,8 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
 
 int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
   ARG(a, "null args");
-  ARG(a->mode == 0 || a->mode == 5, "tp_qkv mode %d is not supported (0 | 5)", a->mode);
+  ARG(a->mode == 0 || a->mode == 5 || a->mode == 8, "tp_qkv mode %d is not supported (0 | 5 | 8)", a->mode);
+  ARG((a->mode == 8) == (a->red != nullptr), "mode 8 (the consumer's CTAs help the owner reducer) needs red, the other modes take none");
   ARG(a->tile == 256 || a->tile == 128 || a->tile == 0, "bad tile %d", a->tile);
   const int bn = a->tile == 128 ? 128 : 256;
   const bool pair = a->cta_pair != 0 && bn == 256;
@@ -500,10 +539,15 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
   p.group_rows = a->swizzle > 0 ? a->swizzle : 1;
   p.tail_cols = 0;
   p.rowss = a->rowss; p.inv_k = 1.0f / static_cast<float>(a->K); p.eps = a->eps;
-  if (a->mode == 5) {
-    ARG(a->panel_flag, "mode 5 needs panel_flag");
+  if (a->mode == 5 || a->mode == 8) {
+    ARG(a->panel_flag, "mode %d needs panel_flag", a->mode);
     p.mode = kModeTpConsumer; p.panel_flag = a->panel_flag;
     p.pdl_wait = 0;            // the per-panel flags carry the dependency on the producer grid
+    if (a->mode == 8) {
+      if (int r = fill_reduce(a->red, p.red, true)) return r;
+      ARG(p.red.unit_ctr, "mode 8 needs red->unit_ctr: the units are shared out through that counter");
+      ARG(p.red.M == a->M && p.red.n1 == a->K, "mode 8: the reducer's shape (M=%d, n1=%d) must be this GEMM's (M=%d, K=%d)", p.red.M, p.red.n1, a->M, a->K);
+    }
   } else {
     p.mode = a->rowss ? kModeTpConsumer : kModePlain;   // mode 0 with rowss: scale only, no waits
     p.panel_flag = nullptr;
@@ -514,101 +558,72 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
 }
 
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
-  ARG(a, "null args");
-  ARG(a->world == 1 || a->world == 2 || a->world == 4 || a->world == 8, "world %d is not supported (1 | 2 | 4 | 8)", a->world);
-  ARG(a->rank >= 0 && a->rank < a->world, "bad rank %d", a->rank);
-  ARG(a->M >= 0 && a->M % 128 == 0 && a->n1 > 0 && a->n1 % 256 == 0, "bad shape M=%d n1=%d", a->M, a->n1);
-  ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
-  ARG(a->tile_flags && a->rowss_local && a->panel_done, "null protocol buffer");
-  ARG(a->tail_cols >= 0 && a->tail_cols <= a->n1 / 256, "bad tail_cols %d", a->tail_cols);
-  GUARD(device);
   ReduceParams p;
-  memset(&p, 0, sizeof(p));
-  p.M = a->M; p.n1 = a->n1; p.rank = a->rank; p.world = a->world;
-  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
-  p.tile_flags = a->tile_flags;
-  for (int d = 0; d < a->world; d++) {
-    ARG(a->inbox[d] && a->peer_x[d] && a->peer_rowss[d] && a->peer_panel_flag[d], "missing peer buffer %d", d);
-    p.inbox[d] = static_cast<const uint4*>(a->inbox[d]);
-    p.x[d] = static_cast<uint4*>(a->peer_x[d]);
-    p.rowss[d] = a->peer_rowss[d];
-    p.panel_flag[d] = a->peer_panel_flag[d];
-  }
-  p.resid = static_cast<const uint4*>(a->resid);
-  p.rowss_local = a->rowss_local; p.panel_done = a->panel_done;
-  p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
-  p.unit_ctr = a->unit_ctr; p.trace = a->trace; p.status = a->status;
-  if (a->x_mc || a->rowss_mc || a->panel_flag_mc) {   // NVLS variant: all three multicast addresses or none
-    ARG(a->x_mc && a->rowss_mc && a->panel_flag_mc, "the NVLS variant needs x_mc, rowss_mc and panel_flag_mc");
-    ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
-    p.x_mc = static_cast<uint4*>(a->x_mc); p.rowss_mc = a->rowss_mc; p.panel_flag_mc = a->panel_flag_mc;
-  }
-  p.limit_ns = limit_ns();
+  if (int r = fill_reduce(a, p, true)) return r;
+  ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
+  GUARD(device);
   if (a->M == 0) return 0;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (a->tma) {   // TMA-fed variant: same protocol, shared-memory staging of the inbox and residual patches
-    ARG(!a->unit_ctr, "the TMA-fed reducer assigns units statically (unit_ctr must be NULL)");
-    switch (a->world) {
-      case 1: return launch_reduce_tma<1>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
-      case 2: return launch_reduce_tma<2>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
-      case 4: return launch_reduce_tma<4>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
-      default: return launch_reduce_tma<8>(p, a->inbox, a->resid, a->panels_per_owner, a->blocks, s);
-    }
-  }
-  switch (a->world) {
-    case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
-    case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);
-    case 4: return launch_reduce<4>(p, a->blocks, a->threads, s);
-    default: return launch_reduce<8>(p, a->blocks, a->threads, s);
-  }
+  return launch_reduce_any(p, a->blocks, a->threads, static_cast<cudaStream_t>(stream));
 }
 
-// The owner reducer for hosts that must not allocate device memory: same arguments and results as ctapp_tp_reduce, but
-// the per-step working memory (row accumulators, panel arrival counters) is the library's own fixed array instead of
-// caller buffers, and this call clears it itself.  args->rowss_local / args->panel_done / args->unit_ctr are ignored.
-// Nothing here allocates: one cudaGetSymbolAddress per device (first call only), two cudaMemsetAsync, one launch.
+// The owner reducer for hosts that must not allocate device memory: same inputs, outputs and results as ctapp_tp_reduce,
+// but the per-step working memory (row accumulators, panel arrival counters) is the library's own fixed array instead of
+// caller buffers, and this call clears it itself.  Nothing here allocates: two cudaMemsetAsync and one launch (plus one
+// cudaGetSymbolAddress per device on the first call, unless ctapp_preload has already run there).
 int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* stream) {
   ARG(a, "null args");
-  ARG(a->world == 1 || a->world == 2 || a->world == 4 || a->world == 8, "world %d is not supported (1 | 2 | 4 | 8)", a->world);
-  ARG(a->rank >= 0 && a->rank < a->world, "bad rank %d", a->rank);
-  ARG(a->M >= 0 && a->M % 128 == 0 && a->n1 > 0 && a->n1 % 256 == 0, "bad shape M=%d n1=%d", a->M, a->n1);
   ARG(a->M <= kNoAllocMaxM, "M=%d is beyond the built-in scratch of ctapp_tp_reduce_noalloc (at most %d rows); use ctapp_tp_reduce with caller buffers",
       a->M, kNoAllocMaxM);
+  // what this variant does not do is refused, not dropped: a caller that set one of these would get other behaviour than it asked for
+  ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc, "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc must be NULL");
+  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL and pdl_trigger 0");
+  ReduceParams p;
+  if (int r = fill_reduce(a, p, false)) return r;
   ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
-  ARG(a->tile_flags, "null tile_flags");
-  ARG(a->tail_cols >= 0 && a->tail_cols <= a->n1 / 256, "bad tail_cols %d", a->tail_cols);
   GUARD(device);
   unsigned char* scratch = nullptr;
   if (int r = noalloc_scratch_ptr(device, &scratch)) return r;
-  ReduceParams p;
-  memset(&p, 0, sizeof(p));
-  p.M = a->M; p.n1 = a->n1; p.rank = a->rank; p.world = a->world;
-  p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
-  p.tile_flags = a->tile_flags;
-  for (int d = 0; d < a->world; d++) {
-    ARG(a->inbox[d] && a->peer_x[d] && a->peer_rowss[d] && a->peer_panel_flag[d], "missing peer buffer %d", d);
-    p.inbox[d] = static_cast<const uint4*>(a->inbox[d]);
-    p.x[d] = static_cast<uint4*>(a->peer_x[d]);
-    p.rowss[d] = a->peer_rowss[d];
-    p.panel_flag[d] = a->peer_panel_flag[d];
-  }
-  p.resid = static_cast<const uint4*>(a->resid);
   p.rowss_local = reinterpret_cast<float*>(scratch);
   p.panel_done = reinterpret_cast<int*>(scratch + kNoAllocRowssBytes);
-  p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
-  p.unit_ctr = nullptr; p.trace = a->trace; p.status = a->status;
-  p.limit_ns = limit_ns();
   if (a->M == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // the array keeps whatever the previous call left: the accumulators and counters of this step's rows start from zero
   CU_OK(cudaMemsetAsync(p.rowss_local, 0, static_cast<size_t>(a->M) * sizeof(float), s));
   CU_OK(cudaMemsetAsync(p.panel_done, 0, static_cast<size_t>(a->M / 128) * sizeof(int), s));
-  switch (a->world) {
-    case 1: return launch_reduce<1>(p, a->blocks, a->threads, s);
-    case 2: return launch_reduce<2>(p, a->blocks, a->threads, s);
-    case 4: return launch_reduce<4>(p, a->blocks, a->threads, s);
-    default: return launch_reduce<8>(p, a->blocks, a->threads, s);
-  }
+  return launch_reduce_any(p, a->blocks, a->threads, s);
+}
+
+// ------------------------------------------------------------------------------------------ read-back of the device-side integer maps
+int ctapp_debug_tile_order(int order, int tiles_m, int tiles_n, int group_rows, int tail_cols, int* out_mn, int device, void* stream) {
+  ARG(order >= 0 && order <= 2 && tiles_m > 0 && tiles_n > 0 && out_mn, "bad arguments");
+  ARG(tail_cols >= 0 && tail_cols <= tiles_n, "bad tail_cols %d", tail_cols);
+  GUARD(device);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.num_tiles = tiles_m * tiles_n;
+  p.order = order; p.group_rows = group_rows; p.tail_cols = tail_cols;
+  tile_order_kernel<<<(p.num_tiles + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(p, out_mn);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_debug_unit_order(int owned_panels, int tiles_n, int tail_cols, int order, int swz, int* out_jnq, int device, void* stream) {
+  ARG(owned_panels > 0 && tiles_n > 0 && tail_cols >= 0 && tail_cols <= tiles_n && (order == 1 || order == 2) && swz >= 0 && out_jnq, "bad arguments");
+  GUARD(device);
+  const int U = owned_panels * tiles_n * 4;
+  unit_order_kernel<<<(U + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(owned_panels, tiles_n, tail_cols, order, swz, out_jnq);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int ctapp_debug_queue_slots(int num_tiles, int tiles_n, int src_group, const int* src_windows, int n_windows, int* out_slots, int device, void* stream) {
+  ARG(num_tiles > 0 && tiles_n > 0 && num_tiles % tiles_n == 0 && out_slots, "bad arguments");
+  GUARD(device);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_n = tiles_n; p.num_tiles = num_tiles; p.src.cap = num_tiles;
+  p.src_group = src_group; p.src_windows = src_windows; p.n_windows = src_windows ? n_windows : 0;
+  queue_slot_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, out_slots);
+  CU_OK(cudaGetLastError());
+  return 0;
 }
 
 int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream) {

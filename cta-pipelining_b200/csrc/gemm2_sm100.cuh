@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
   if (p.pdl_trigger) pdl_launch_dependents();
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
+  if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch);   // every warp, before it takes up its role
 
   // a give-up in one CTA stops both
   auto abort_pair = [&](int code) {
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         int mp, n;
         if (p.mode == kModeChain) { mp = tile / p.tiles_n; n = tile - mp * p.tiles_n; } else decode_tile(p, tile, mp, n);
         const int m = 2 * mp + static_cast<int>(crank);   // this CTA's 128-row panel
+        if (p.tile_log && leader) p.tile_log[1 + atomicAdd(p.tile_log, 1)] = (mp << 16) | n;
         if (p.stamps && ntiles_done == 0) p.stamps[blockIdx.x * 8 + 1] = globaltimer();
         if (p.mode == kModeChain && !p.skip_wait) fence_proxy_async_global();   // peer-written A rows vs the TMA loads below
         if (p.mode == kModeTpConsumer && p.panel_flag && m < p.panels && !(m < 128 && (panel_seen[m >> 5] >> (m & 31) & 1u))) {
@@ -162,6 +164,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         const uint32_t full0 = mapa_u32(full, 0);   // the leader's full[0] as a cluster address; stages are 8 bytes apart
         next = -2;
         for (int kb = 0; kb < KB; kb++) {
+          // k-chunk dependencies: the flag covers the pair's 256 rows; each CTA asks for itself before it loads its half
+          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && !wait_chunk(p, mp, kb, limit)) { abort_pair(kStatusTimeoutChunk); ok = false; break; }
           if (!mbar_wait(empty + stage, phase ^ 1, s_abort, limit)) { ok = false; break; }
           if (leader) mbar_arrive_expect_tx(full + stage, 2 * Cfg::kStageBytes);   // both CTAs' bytes are counted here
           tma_load_2d_pair(sA + stage * Cfg::kABytes, &p.tmA, kb * BK, m * BM, full0 + stage * 8);
@@ -346,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
       if (p.stamps && threadIdx.x == 64) p.stamps[blockIdx.x * 8 + 3] = globaltimer();
 
       // ---- publish
-      const bool chain_signal = p.mode == kModeChain && p.dep_offsets != nullptr;
+      const bool chain_signal = p.mode == kModeChain && (p.dep_offsets != nullptr || p.chunk_dst != nullptr);
       if (chain_signal || (p.mode == kModeTpProducer && valid)) {
         if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); mbar_arrive(epi); }
         if (ew == 0) {
@@ -373,7 +377,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
             }
             if (!__shfl_sync(0xffffffffu, okp, 0)) break;
             fence_acq_rel_sys();
-            const int begin = p.dep_offsets[tile], deg = p.dep_offsets[tile + 1] - begin;
+            if (p.chunk_dst && lane == 0) st_relaxed_sys(p.chunk_dst + tile, p.chunk_value);   // tile == mp * tiles_n + n
+            const int begin = p.dep_offsets ? p.dep_offsets[tile] : 0, deg = p.dep_offsets ? p.dep_offsets[tile + 1] - begin : 0;
             for (int i0 = 0; i0 < deg; i0 += 32) {
               const int i = i0 + lane;
               int old = 0, c = 0;

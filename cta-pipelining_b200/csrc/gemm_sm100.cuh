@@ -13,6 +13,7 @@
 // Every wait on another GPU is bounded; a give-up is reported in the status buffer and the CTA drains and exits.
 #pragma once
 #include "ptx.cuh"
+#include "reduce_sm100.cuh"
 
 namespace ctapp {
 
@@ -30,7 +31,7 @@ enum GemmMode : int {
   kModeChain = 1,        // tile ids from a work queue; optional downstream signalling
   kModeTpProducer = 7,   // scatter tile (m, n) to owner m % world and raise its tile flag
   kModeTpConsumer = 5,   // wait per 128-row panel for the owner's panel flag; scale rows by rsqrt(rowss/K + eps)
-};
+};                       // (with red.unit_ctr set its CTAs first help the owner reducer: every warp claims units until none are left)
 enum TileOrder : int { kOrderGrouped = 0, kOrderMFastTail = 1, kOrderNFast = 2 };
 
 struct Queue { int* entries; int* head; int* tail; int cap; };
@@ -53,6 +54,12 @@ struct alignas(64) GemmParams {
   const int* src_windows;
   const int* dst_ready;
   int ready_value;
+  // chain, k-chunk dependencies: instead of (or beside) the scoreboard, a finished tile (m, n) raises chunk_dst[m * tiles_n + n]
+  // = chunk_value in the next GPU's memory; a consuming GEMM waits for chunk_src[m * chunk_cols + c] >= chunk_value before it
+  // loads the k-blocks [c * chunk_kblocks, (c + 1) * chunk_kblocks) of a tile of row m: its main loop streams behind the producer
+  int* chunk_dst;
+  const int* chunk_src;
+  int chunk_kblocks, chunk_cols, chunk_value;
   // tensor-parallel boundary
   int world, rank, ppo;
   int* peer_tile_flags[kMaxWorld];
@@ -67,19 +74,22 @@ struct alignas(64) GemmParams {
   int act;                         // CTA-pair kernel only: 1 = silu(gate) * up epilogue over interleaved 128-column halves
   int* status;
   unsigned long long* stamps;      // 8 u64 per CTA or null
+  int* tile_log;                   // null, or [0] = count followed by one packed (m << 16 | n) per scheduled tile, in schedule order
   long long limit_ns;
+  ReduceParams red;                // tensor-parallel consumer: the owner reducer's arguments when its CTAs help (red.unit_ctr != null)
 };
 
-template <int BN> struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr uint32_t kABytes = BM * BK * 2;
-  static constexpr uint32_t kBBytes = BN * BK * 2;
-  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kEpiBytes = 4 * 2 * kStageRows * kStoreCols * 2;   // 4 warps x 2 buffers x 4 KB
-  static constexpr uint32_t kBarBytes = 512;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;   // + alignment slack
-  static constexpr uint32_t kTmemCols = 2 * BN;
-};
+// Bounded wait of a consuming GEMM for one k-chunk of its A rows (written by the previous GPU's epilogue).
+__device__ __forceinline__ bool wait_chunk(const GemmParams& p, int m, int kb, long long limit) {
+  int seen;
+  const int idx = m * p.chunk_cols + kb / p.chunk_kblocks;
+  if (!spin_acquire_sys(p.chunk_src + idx, PredGe{p.chunk_value}, limit, seen)) {
+    report_status(p.status, kStatusTimeoutChunk, idx, p.chunk_value, seen);
+    return false;
+  }
+  fence_proxy_async_global();   // the rows were written through another GPU's async proxy; the loads below go through this one's
+  return true;
+}
 
 // Chain mode: which slot of the source queue the idx-th pop reads.  The producer publishes a finished row panel as tiles_n
 // consecutive slots.  With windows the pops walk a window of g such panels n-tile major (slot 0 of every panel of the
@@ -120,6 +130,33 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int L, int& m, 
   const int rows = min(g, TM - m0), r = L - grp * per;
   n = r / rows; m = m0 + (r - n * rows);
 }
+
+// Read-back of the static tile order: out[2 L], out[2 L + 1] = (m, n) of schedule position L.
+__global__ void tile_order_kernel(GemmParams p, int* out) {
+  for (int L = blockIdx.x * blockDim.x + threadIdx.x; L < p.num_tiles; L += gridDim.x * blockDim.x) {
+    int m, n;
+    decode_tile(p, L, m, n);
+    out[2 * L] = m; out[2 * L + 1] = n;
+  }
+}
+// Read-back of the pop order of a consuming chain stage: out[i] = queue slot of the i-th pop.
+__global__ void queue_slot_kernel(GemmParams p, int* out) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int cur = 0;
+    for (int i = 0; i < p.num_tiles; i++) out[i] = queue_slot(p, i, cur);
+  }
+}
+
+template <int BN> struct GemmCfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr uint32_t kABytes = BM * BK * 2;
+  static constexpr uint32_t kBBytes = BN * BK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kEpiBytes = 4 * 2 * kStageRows * kStoreCols * 2;   // 4 warps x 2 buffers x 4 KB
+  static constexpr uint32_t kBarBytes = 512;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;   // + alignment slack
+  static constexpr uint32_t kTmemCols = 2 * BN;
+};
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
@@ -168,6 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (p.pdl_trigger) pdl_launch_dependents();
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
+  if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch);   // every warp, before it takes up its role
 
   if (warp == 0) {
     // ============================================================ scheduler + TMA loader
@@ -206,6 +244,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (tile < 0) break;
         int m, n;
         if (p.mode == kModeChain) { m = tile / p.tiles_n; n = tile - m * p.tiles_n; } else decode_tile(p, tile, m, n);
+        if (p.tile_log) p.tile_log[1 + atomicAdd(p.tile_log, 1)] = (m << 16) | n;
         if (p.stamps && ntiles_done == 0) { p.stamps[blockIdx.x * 8 + 1] = globaltimer(); }
         if (p.mode == kModeTpConsumer && p.panel_flag && !(m < 128 && (panel_seen[m >> 5] >> (m & 31) & 1u))) {
           int seen;
@@ -217,6 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         next = -2;
         for (int kb = 0; kb < KB; kb++) {
+          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && !wait_chunk(p, m, kb, limit)) { *s_abort = kStatusTimeoutChunk; ok = false; break; }
           if (!mbar_wait(empty + stage, phase ^ 1, s_abort, limit)) { ok = false; break; }
           mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
           tma_load_2d(sA + stage * Cfg::kABytes, &p.tmA, kb * BK, m * BM, full + stage);
@@ -372,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       if (p.stamps && threadIdx.x == 64) p.stamps[blockIdx.x * 8 + 3] = globaltimer();
 
       // ---- publish the tile
-      const bool chain_signal = p.mode == kModeChain && p.dep_offsets != nullptr;
+      const bool chain_signal = p.mode == kModeChain && (p.dep_offsets != nullptr || p.chunk_dst != nullptr);
       if (chain_signal || p.mode == kModeTpProducer) {
         if (lane == 0) { bulk_wait<0>(); fence_proxy_async(); mbar_arrive(epi); }   // this warp's rows have reached the destination
         if (ew == 0) {
@@ -385,6 +425,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
               st_relaxed_sys(p.peer_tile_flags[dst] + (p.rank * p.ppo + m / p.world) * p.tiles_n + n, epoch);
             }
           } else {
+            if (p.chunk_dst && lane == 0) st_relaxed_sys(p.chunk_dst + tile, p.chunk_value);   // tile == m * tiles_n + n
+            if (p.dep_offsets) {
             const int begin = p.dep_offsets[tile], deg = p.dep_offsets[tile + 1] - begin;
             for (int i0 = 0; i0 < deg; i0 += 32) {
               const int i = i0 + lane;
@@ -410,6 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const int slot = atom_add_relaxed_sys(p.dst.tail, 1);
                 st_release_sys(p.dst.entries + slot % p.dst.cap, c);
               }
+            }
             }
           }
           if (p.stamps && lane == 0) p.stamps[blockIdx.x * 8 + 4] = globaltimer();

@@ -18,6 +18,7 @@ enum : int {
   kStatusTimeoutPipe = 5,       // an intra-CTA pipeline barrier never completed (follow-on of another code)
   kStatusTimeoutProbe = 6,      // probe kernels (ping-pong, ordering stress)
   kStatusBadIndex = 7,          // a queue entry / flag index outside its table
+  kStatusTimeoutChunk = 8,      // k-chunk flag (chain with k-chunk dependencies) never arrived
 };
 // status buffer layout (ints): [0] code  [1] block  [2] what (index waited on)  [3] expected  [4] seen  [5] count of CTAs that gave up
 constexpr int kStatusInts = 8;

@@ -25,23 +25,59 @@ struct ReduceParams {
   float* rowss_local;
   int* panel_done;
   int ppo, tail;
-  int* unit_ctr;
+  int order, swz;            // unit order when tail == 0: 1 = m fastest in groups of swz n-tiles, 2 = panel by panel
+  int* unit_ctr;             // non-null: units are claimed from this counter (shared with consumer CTAs that help)
+  int* unit_log;             // non-null: [0] = count, then one packed (j << 16 | n << 2 | q) per processed unit, in claim order
   unsigned long long* trace;
   int* status;
   long long limit_ns;
+  int pdl_trigger;           // raise the programmatic-launch trigger at entry (the producer GEMM is this kernel's dependent)
   // NVLS variant: multicast addresses of the x buffer, the row-sum buffer and the panel flags (null = unicast pushes)
   uint4* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
 };
 
-// unit u -> (owned panel j, n-tile, quarter), following the producer order "m-fast head, panel-major tail"
-__device__ __forceinline__ void unit_map(int u, int Pr, int tiles_n, int tail, int& j, int& n, int& q) {
+// Unit u -> (owned panel j, n-tile, quarter).  The order follows the producer's tile order so that units become ready in
+// the order they are visited:
+//   tail > 0            m-fast head over the first tiles_n - tail n-tiles, then panel-major over the last `tail` n-tiles
+//   order 1, swz <= 1   n-major: for each n-tile, every owned panel
+//   order 1, swz > 1    groups of swz n-tiles: for each group, for each owned panel, the group's n-tiles
+//   order 2             panel by panel
+// Same integer function as the reference's red5_map (csrc/ctapp_tp4.cuh:551-565) with the n-tile count as a parameter.
+__device__ __forceinline__ void unit_map(int u, int Pr, int tiles_n, int tail, int order, int swz, int& j, int& n, int& q) {
   q = u & 3;
   const int t = u >> 2;
-  const int head = Pr * (tiles_n - tail);
-  if (t < head) { n = t / Pr; j = t - n * Pr; }
-  else { const int t2 = t - head; j = t2 / tail; n = tiles_n - tail + (t2 - j * tail); }
+  if (tail > 0) {
+    const int head = Pr * (tiles_n - tail);
+    if (t < head) { n = t / Pr; j = t - n * Pr; }
+    else { const int t2 = t - head; j = t2 / tail; n = tiles_n - tail + (t2 - j * tail); }
+    return;
+  }
+  if (order == 2) { j = t / tiles_n; n = t - j * tiles_n; return; }
+  if (swz <= 1) { n = t / Pr; j = t - n * Pr; return; }
+  const int g = t / swz;
+  j = g % Pr;
+  n = (g / Pr) * swz + t % swz;
+}
+
+// acc + (low | high) half of a packed bf16 pair, in fp32: the conversion is part of the add (sm_100 mixed-precision add)
+__device__ __forceinline__ float add_bf16_lo(float acc, uint32_t v) {
+  float d;
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %1;\n\t}" : "=f"(d) : "f"(acc), "r"(v));
+  return d;
+}
+__device__ __forceinline__ float add_bf16_hi(float acc, uint32_t v) {
+  float d;
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, hi, %1;\n\t}" : "=f"(d) : "f"(acc), "r"(v));
+  return d;
+}
+// acc + h * h for both halves of a packed bf16 pair
+__device__ __forceinline__ float sq_bf16x2(float acc, uint32_t v) {
+  float d;
+  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 t;\n\tmov.b32 {lo, hi}, %2;\n\tfma.rn.f32.bf16 t, lo, lo, %1;\n\tfma.rn.f32.bf16 %0, hi, hi, t;\n\t}"
+      : "=f"(d) : "f"(acc), "r"(v));
+  return d;
 }
 
 __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
@@ -52,113 +88,180 @@ __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
   return s;
 }
 
-// MC: the pushes to every rank (x rows, row sums, panel flags) are single multimem stores on a multicast address, replicated
-// by the NVSwitch, instead of one unicast store per rank; everything else is the same kernel.
-template <int W, int ROWS, bool MC = false>
-__global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p) {
-  const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
+// One unit, by one warp: 32 rows x 256 columns of x.  Returns false when a tile flag never arrived (status written).
+//   * lanes 0..W-1 wait (bounded) for the W tile flags of the unit's tile
+//   * per batch of ROWS rows: every lane loads its 16 bytes of every source and of the residual, adds them in fp32 in slot
+//     order (the residual last) starting from -0.0 so that the first add is exact, rounds once to bf16, pushes the 16 bytes
+//     to every rank (remote copies first, the local one last; or one multimem store), and squares the ROUNDED values
+//   * the ROWS row sums are folded across the warp by halving (ROWS values -> one per lane group) and added to rowss_local
+//     by ROWS lanes at once
+//   * lane 0 orders everything above before the panel's arrival count; the warp that completes the panel pushes the panel's
+//     128 row sums and then panel_flag[m] = epoch to every rank
+template <int W, int ROWS, bool MC>
+__device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, int u, int Pr, int tiles_n, int lane) {
+  static_assert(ROWS == 1 || ROWS == 2 || ROWS == 4, "rows per batch");
+  int j, n, q;
+  unit_map(u, Pr, tiles_n, p.tail, p.order, p.swz, j, n, q);
+  if (p.unit_log && lane == 0) p.unit_log[1 + atomicAdd(p.unit_log, 1)] = (j << 16) | (n << 2) | q;
+  bool ok = true;
+  if (lane < W) {
+    int seen;
+    const int idx = (lane * p.ppo + j) * tiles_n + n;
+    if (!spin_acquire_sys(p.tile_flags + idx, PredGe{epoch}, p.limit_ns, seen)) {
+      report_status(p.status, kStatusTimeoutTile, idx, epoch, seen);
+      ok = false;
+    }
+  }
+  if (!__all_sync(0xffffffffu, ok)) return false;
+  const int row_vecs = p.n1 / 8;                 // 16-byte vectors per row
+  const int m = j * W + p.rank;
+  const int xrow0 = m * 128 + q * 32;
+  // every source slice has the same geometry: one running offset serves all of them (the bases sit in the parameter bank)
+  size_t ioff = static_cast<size_t>(j * 128 + q * 32) * row_vecs + n * 32 + lane;
+  size_t xoff0 = static_cast<size_t>(xrow0) * row_vecs + n * 32 + lane;
+  const bool rsrc = p.resid != nullptr;
+#pragma unroll 1
+  for (int r = 0; r < 32; r += ROWS, ioff += static_cast<size_t>(ROWS) * row_vecs, xoff0 += static_cast<size_t>(ROWS) * row_vecs) {
+    uint4 part[ROWS][W], res[ROWS];
+#pragma unroll
+    for (int rr = 0; rr < ROWS; rr++) {
+#pragma unroll
+      for (int s = 0; s < W; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
+    }
+    if (rsrc) {
+#pragma unroll
+      for (int rr = 0; rr < ROWS; rr++) res[rr] = __ldg(p.resid + xoff0 + rr * row_vecs);
+    }
+    float ss[ROWS];
+#pragma unroll
+    for (int rr = 0; rr < ROWS; rr++) {
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float lo = -0.0f, hi = -0.0f;
+#pragma unroll
+        for (int s = 0; s < W; s++) { const uint32_t w = (&part[rr][s].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
+        if (rsrc) { const uint32_t w = (&res[rr].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
+        o[i] = pack_bf16x2(lo, hi);
+      }
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      const size_t xoff = xoff0 + rr * row_vecs;
+      if (MC) {
+        multimem_st_v4(p.x_mc + xoff, ov);
+      } else {
+#pragma unroll
+        for (int d = 1; d <= W; d++) st_relaxed_sys_v4(p.x[(p.rank + d) % W] + xoff, ov);
+      }
+      ss[rr] = sq_bf16x2(sq_bf16x2(sq_bf16x2(sq_bf16x2(0.f, o[0]), o[1]), o[2]), o[3]);
+    }
+    // fold ROWS sums across the warp: after the halving steps lane l holds (part of) row (l / (32 / ROWS))'s sum
+    float v;
+    if (ROWS == 4) {
+      const bool up = lane & 16;
+      float k0 = up ? ss[2] : ss[0], k1 = up ? ss[3] : ss[1];
+      k0 += __shfl_xor_sync(0xffffffffu, up ? ss[0] : ss[2], 16);
+      k1 += __shfl_xor_sync(0xffffffffu, up ? ss[1] : ss[3], 16);
+      const bool up8 = lane & 8;
+      v = (up8 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, up8 ? k0 : k1, 8);
+#pragma unroll
+      for (int sh = 4; sh > 0; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+      if ((lane & 7) == 0) atomicAdd(p.rowss_local + xrow0 + r + (lane >> 3), v);
+    } else if (ROWS == 2) {
+      const bool up = lane & 16;
+      v = (up ? ss[1] : ss[0]) + __shfl_xor_sync(0xffffffffu, up ? ss[0] : ss[1], 16);
+#pragma unroll
+      for (int sh = 8; sh > 0; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+      if ((lane & 15) == 0) atomicAdd(p.rowss_local + xrow0 + r + (lane >> 4), v);
+    } else {
+      v = ss[0];
+#pragma unroll
+      for (int sh = 16; sh > 0; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+      if (lane == 0) atomicAdd(p.rowss_local + xrow0 + r, v);
+    }
+  }
+  __syncwarp();
+  const int units_per_panel = tiles_n * 4;
+  int last = 0;
+  if (lane == 0) {
+    fence_acq_rel_sys();   // this warp's x stores and row-sum atomics before the arrival count
+    last = atom_add_relaxed_gpu(p.panel_done + m, 1) == units_per_panel - 1;
+  }
+  if (__shfl_sync(0xffffffffu, last, 0)) {
+    if (lane == 0) fence_acq_rel_sys();   // acquire side: the other warps' stores and atomics of this panel
+    __syncwarp();
+    const float4 sums = __ldcg(reinterpret_cast<const float4*>(p.rowss_local + m * 128) + lane);
+    if (MC) {
+      multimem_st_f32x4(p.rowss_mc + m * 128 + lane * 4, sums);
+    } else {
+#pragma unroll
+      for (int d = 1; d <= W; d++) st_relaxed_sys_f32x4(p.rowss[(p.rank + d) % W] + m * 128 + lane * 4, sums);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      fence_acq_rel_sys();   // x (all warps, through the arrival chain) and the row sums before the flags
+      if (MC) {
+        multimem_st_release_b32(p.panel_flag_mc + m, epoch);
+      } else {
+#pragma unroll
+        for (int d = 1; d <= W; d++) st_relaxed_sys(p.panel_flag[(p.rank + d) % W] + m, epoch);
+      }
+      if (p.trace) p.trace[m] = globaltimer();
+    }
+    __syncwarp();
+  }
+  return true;
+}
+
+// The unit loop of one warp.  Static assignment: unit = first, first + stride, ...; with p.unit_ctr every warp claims its
+// next unit from the shared counter instead (first / stride unused), which lets CTAs of another kernel join in.
+template <int W, int ROWS, bool MC>
+__device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, int first, int stride, int lane) {
   const int P = p.M / 128;
   const int Pr = P > p.rank ? (P - 1 - p.rank) / W + 1 : 0;
   const int tiles_n = p.n1 / 256;
-  const int units_per_panel = tiles_n * 4;
-  const int U = Pr * units_per_panel;
-  const int row_vecs = p.n1 / 8;                 // uint4 per row
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int stride = gridDim.x * nwarps;
+  const int U = Pr * tiles_n * 4;
   auto claim = [&]() -> int {
     int v = 0;
     if (lane == 0) v = atomicAdd(p.unit_ctr, 1);
     return __shfl_sync(0xffffffffu, v, 0);
   };
-  for (int u = p.unit_ctr ? claim() : warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x); u < U;
-       u = p.unit_ctr ? claim() : u + stride) {
+  for (int u = p.unit_ctr ? claim() : first; u < U; u = p.unit_ctr ? claim() : u + stride)
+    if (!reduce_unit<W, ROWS, MC>(p, epoch, u, Pr, tiles_n, lane)) return;   // a producer never delivered: the host reads the status
+}
+
+// rows per batch: as many as the register file of a 1024-thread CTA allows (64 registers per thread)
+template <int W> struct RedRows { static constexpr int value = W >= 8 ? 1 : (W >= 2 ? 2 : 4); };
+
+// MC: the pushes to every rank (x rows, row sums, panel flags) are single multimem stores on a multicast address, replicated
+// by the NVSwitch, instead of one unicast store per rank; everything else is the same kernel.
+template <int W, int ROWS, bool MC = false>
+__global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p) {
+  if (p.pdl_trigger) pdl_launch_dependents();
+  const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  reduce_units<W, ROWS, MC>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x) * nwarps, lane);
+}
+
+// Consumer CTAs helping the owner reducer (any CTA shape): every warp claims units until none are left.
+__device__ __forceinline__ void reduce_help(const ReduceParams& p, int epoch) {
+  const int lane = threadIdx.x & 31;
+  if (!p.unit_ctr) return;
+  const bool mc = p.x_mc != nullptr;
+  switch (p.world) {
+    case 1: reduce_units<1, 4, false>(p, epoch, 0, 0, lane); break;
+    case 2: if (mc) reduce_units<2, 2, true>(p, epoch, 0, 0, lane); else reduce_units<2, 2, false>(p, epoch, 0, 0, lane); break;
+    case 4: if (mc) reduce_units<4, 2, true>(p, epoch, 0, 0, lane); else reduce_units<4, 2, false>(p, epoch, 0, 0, lane); break;
+    default: if (mc) reduce_units<8, 1, true>(p, epoch, 0, 0, lane); else reduce_units<8, 1, false>(p, epoch, 0, 0, lane); break;
+  }
+}
+
+// Read-back of the unit order: out[3 u .. 3 u + 2] = (j, n, q) for every unit of a rank with Pr owned panels.
+__global__ void unit_order_kernel(int Pr, int tiles_n, int tail, int order, int swz, int* out) {
+  const int U = Pr * tiles_n * 4;
+  for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < U; u += gridDim.x * blockDim.x) {
     int j, n, q;
-    unit_map(u, Pr, tiles_n, p.tail, j, n, q);
-    bool ok = true;
-    if (lane < W) {
-      int seen;
-      const int idx = (lane * p.ppo + j) * tiles_n + n;
-      if (!spin_acquire_sys(p.tile_flags + idx, PredGe{epoch}, p.limit_ns, seen)) {
-        report_status(p.status, kStatusTimeoutTile, idx, epoch, seen);
-        ok = false;
-      }
-    }
-    if (!__all_sync(0xffffffffu, ok)) return;   // a producer never delivered: give up (bounded), the host reads the status
-    const int m = j * W + p.rank;
-    const int xrow0 = m * 128 + q * 32;
-    const size_t ioff0 = static_cast<size_t>(j * 128 + q * 32) * row_vecs + n * 32 + lane;
-    const size_t xoff0 = static_cast<size_t>(xrow0) * row_vecs + n * 32 + lane;
-#pragma unroll 1
-    for (int r = 0; r < 32; r += ROWS) {
-      uint4 a[ROWS][W], rv[ROWS];
-#pragma unroll
-      for (int rr = 0; rr < ROWS; rr++) {
-#pragma unroll
-        for (int s = 0; s < W; s++) a[rr][s] = __ldcg(p.inbox[s] + ioff0 + static_cast<size_t>(r + rr) * row_vecs);
-      }
-#pragma unroll
-      for (int rr = 0; rr < ROWS; rr++)
-        rv[rr] = p.resid ? __ldg(p.resid + xoff0 + static_cast<size_t>(r + rr) * row_vecs) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int rr = 0; rr < ROWS; rr++) {
-        uint32_t o[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          float lo = 0.f, hi = 0.f;
-#pragma unroll
-          for (int s = 0; s < W; s++) {
-            const float2 f = unpack_bf16x2((&a[rr][s].x)[i]);
-            if (s == 0) { lo = f.x; hi = f.y; } else { lo += f.x; hi += f.y; }
-          }
-          const float2 fr = unpack_bf16x2((&rv[rr].x)[i]);
-          o[i] = pack_bf16x2(lo + fr.x, hi + fr.y);
-        }
-        const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-        const size_t xoff = xoff0 + static_cast<size_t>(r + rr) * row_vecs;
-        if (MC) {
-          multimem_st_v4(p.x_mc + xoff, ov);
-        } else {
-#pragma unroll
-          for (int d = 1; d <= W; d++) {   // remote copies first, the local one last
-            const int dst = (p.rank + d) % W;
-            st_relaxed_sys_v4(p.x[dst] + xoff, ov);
-          }
-        }
-        float ss = sumsq_bf16x8(ov);
-#pragma unroll
-        for (int sh = 16; sh > 0; sh >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sh);
-        if (lane == 0) atomicAdd(p.rowss_local + xrow0 + r + rr, ss);
-      }
-    }
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      fence_acq_rel_sys();   // this warp's x stores and row-sum atomics before the arrival count
-      last = atom_add_relaxed_gpu(p.panel_done + m, 1) == units_per_panel - 1;
-    }
-    if (__shfl_sync(0xffffffffu, last, 0)) {
-      if (lane == 0) fence_acq_rel_sys();   // acquire side: the other warps' stores and atomics of this panel
-      __syncwarp();
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.rowss_local + m * 128) + lane);
-      if (MC) {
-        multimem_st_f32x4(p.rowss_mc + m * 128 + lane * 4, v);
-      } else {
-#pragma unroll
-        for (int d = 1; d <= W; d++) st_relaxed_sys_f32x4(p.rowss[(p.rank + d) % W] + m * 128 + lane * 4, v);
-      }
-      __syncwarp();
-      if (lane == 0) {
-        fence_acq_rel_sys();   // x (all warps, through the arrival chain) and the row sums before the flags
-        if (MC) {
-          multimem_st_release_b32(p.panel_flag_mc + m, epoch);
-        } else {
-#pragma unroll
-          for (int d = 1; d <= W; d++) st_relaxed_sys(p.panel_flag[(p.rank + d) % W] + m, epoch);
-        }
-        if (p.trace) p.trace[m] = globaltimer();
-      }
-      __syncwarp();
-    }
+    unit_map(u, Pr, tiles_n, tail, order, swz, j, n, q);
+    out[3 * u] = j; out[3 * u + 1] = n; out[3 * u + 2] = q;
   }
 }
 

@@ -21,16 +21,16 @@ CSRC = os.path.join(ROOT, "csrc")
 LIB_PATH = os.path.join(ROOT, "libctapp_b200.so")
 BD = BD4 = ROOT   # build directory (the reference kept one per module; here one library serves both)
 SOURCES = ["ctapp_b200.cu"]
-HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", "reduce_tma_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
+HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-ABI_VERSION = 2
+ABI_VERSION = 3
 STATUS_INTS = 8
 MAX_WORLD = 8
 
 STATUS_TEXT = {1: "source work-queue entry never arrived", 2: "panel flag never arrived", 3: "tile flag never arrived",
                4: "downstream ready flag never arrived", 5: "intra-CTA pipeline barrier never completed",
-               6: "probe wait gave up", 7: "index outside its table"}
+               6: "probe wait gave up", 7: "index outside its table", 8: "k-chunk flag never arrived"}
 
 
 def _nvcc():
@@ -82,7 +82,8 @@ class ChainArgs(C.Structure):
                 ("scoreboard", C.c_void_p), ("dst", Queue), ("tiles_n", C.c_int), ("skip_wait", C.c_int), ("fence", C.c_int),
                 ("tiles_n2", C.c_int), ("rowpanel", C.c_int), ("dst_ready", C.c_void_p), ("ready_value", C.c_int),
                 ("status", C.c_void_p), ("sms", C.c_int), ("src_group", C.c_int),
-                ("src_windows", C.c_void_p), ("n_windows", C.c_int)]
+                ("src_windows", C.c_void_p), ("n_windows", C.c_int),
+                ("chunk_dst", C.c_void_p), ("chunk_src", C.c_void_p), ("chunk_kblocks", C.c_int), ("chunk_cols", C.c_int), ("chunk_value", C.c_int)]
 
 
 class TpDownArgs(C.Structure):
@@ -91,14 +92,14 @@ class TpDownArgs(C.Structure):
                 ("epoch", C.c_int), ("epoch_dev", C.c_void_p), ("dst_ptrs", C.c_void_p * MAX_WORLD), ("dst_rows", C.c_int),
                 ("peer_tile_flags", C.c_void_p * MAX_WORLD), ("panels_per_owner", C.c_int), ("sms", C.c_int),
                 ("pdl_trigger", C.c_int), ("pdl", C.c_int), ("tail_cols", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p),
-                ("cta_pair", C.c_int)]
+                ("cta_pair", C.c_int), ("tile_log", C.c_void_p)]
 
 
 class TpQkvArgs(C.Structure):
     _fields_ = [("X", C.c_void_p), ("W", C.c_void_p), ("Y", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
                 ("raster", C.c_int), ("swizzle", C.c_int), ("mode", C.c_int), ("epoch", C.c_int), ("epoch_dev", C.c_void_p),
                 ("panel_flag", C.c_void_p), ("rowss", C.c_void_p), ("eps", C.c_float), ("sms", C.c_int), ("pdl", C.c_int),
-                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p), ("cta_pair", C.c_int), ("act", C.c_int)]
+                ("tile", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p), ("cta_pair", C.c_int), ("act", C.c_int), ("red", C.c_void_p)]
 
 
 class TpReduceArgs(C.Structure):
@@ -106,8 +107,9 @@ class TpReduceArgs(C.Structure):
                 ("blocks", C.c_int), ("threads", C.c_int), ("tile_flags", C.c_void_p), ("inbox", C.c_void_p * MAX_WORLD),
                 ("resid", C.c_void_p), ("peer_x", C.c_void_p * MAX_WORLD), ("peer_rowss", C.c_void_p * MAX_WORLD),
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
-                ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("unit_ctr", C.c_void_p), ("trace", C.c_void_p),
-                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("tma", C.c_int)]
+                ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("order", C.c_int), ("swz", C.c_int), ("unit_ctr", C.c_void_p),
+                ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("trace", C.c_void_p),
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p)]
 
 
 _SIGS = {
@@ -140,6 +142,9 @@ _SIGS = {
     "ctapp_tp_qkv": (C.c_int, [C.POINTER(TpQkvArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_reduce": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
     "ctapp_tp_reduce_noalloc": (C.c_int, [C.POINTER(TpReduceArgs), C.c_int, C.c_void_p]),
+    "ctapp_debug_tile_order": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "ctapp_debug_unit_order": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "ctapp_debug_queue_slots": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "ctapp_tp_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "ctapp_mm_red_u32": (C.c_int, [C.c_void_p, C.c_int, C.c_uint, C.c_int, C.c_void_p]),
     "ctapp_mm_red_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
@@ -249,7 +254,8 @@ class ChainModule:
 
     def ctapp_gemm(self, X, W, Y, config_id, src_entries, src_head, src_tail, dep_offsets, dep_consumers, scoreboard,
                    dst_entries, dst_head, dst_tail, tiles_n, skip_wait, fence, stamps=None, tiles_n2=0, rowpanel=0,
-                   status=None, dst_ready=None, ready_value=0, sms=0, src_group=0, src_windows=None):
+                   status=None, dst_ready=None, ready_value=0, sms=0, src_group=0, src_windows=None,
+                   chunk_dst=None, chunk_src=None, chunk_kblocks=0, chunk_value=0):
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
         M, K = X.shape
         N = W.shape[0]
@@ -267,6 +273,11 @@ class ChainModule:
         a.status, a.sms, a.src_group = _ptr(status), int(sms), int(src_group)
         if src_windows is not None:      # int32 device tensor of window offsets in row panels: [0, ..., panels]
             a.src_windows, a.n_windows = _ptr(_i32(src_windows, "src_windows")), src_windows.numel() - 1
+        # k-chunk dependencies: chunk_dst = the next GPU's flags (one per tile of this GEMM); chunk_src = this GPU's flags, a 2-D
+        # int32 tensor (row tiles, producer n-tiles), with chunk_kblocks 64-wide k-blocks per flag
+        a.chunk_dst, a.chunk_value = _ptr(_i32(chunk_dst, "chunk_dst", True)), int(chunk_value)
+        if chunk_src is not None:
+            a.chunk_src, a.chunk_kblocks, a.chunk_cols = _ptr(_i32(chunk_src, "chunk_src")), int(chunk_kblocks), chunk_src.shape[-1]
         dev = X.device.index
         _check(self.lib.ctapp_chain_gemm(_ptr(X), _ptr(W), _ptr(Y), M, N, K, int(config_id), C.byref(a), dev, _stream(dev)))
 
@@ -303,6 +314,26 @@ class ChainModule:
 
     def preload(self, device):
         _check(self.lib.ctapp_preload(int(device)))
+
+    # ---- read-back of the device-side integer maps
+    def debug_tile_order(self, order, tiles_m, tiles_n, group_rows=0, tail_cols=0, device=0):
+        """(tiles, 2) int32 CPU tensor: the (m, n) the kernels' ``decode_tile`` gives for every schedule position."""
+        out = torch.empty(tiles_m * tiles_n, 2, dtype=torch.int32, device=torch.device("cuda", device))
+        _check(self.lib.ctapp_debug_tile_order(int(order), int(tiles_m), int(tiles_n), int(group_rows), int(tail_cols), _ptr(out), device, _stream(device)))
+        return out.cpu()
+
+    def debug_unit_order(self, owned_panels, tiles_n, tail_cols=0, order=1, swz=1, device=0):
+        """(units, 3) int32 CPU tensor: the (j, n, q) the owner reducer's ``unit_map`` gives for every unit."""
+        out = torch.empty(owned_panels * tiles_n * 4, 3, dtype=torch.int32, device=torch.device("cuda", device))
+        _check(self.lib.ctapp_debug_unit_order(int(owned_panels), int(tiles_n), int(tail_cols), int(order), int(swz), _ptr(out), device, _stream(device)))
+        return out.cpu()
+
+    def debug_queue_slots(self, num_tiles, tiles_n, src_group=0, src_windows=None, device=0):
+        """int32 CPU tensor: the queue slot the kernels' ``queue_slot`` reads at every pop."""
+        out = torch.empty(num_tiles, dtype=torch.int32, device=torch.device("cuda", device))
+        nw = src_windows.numel() - 1 if src_windows is not None else 0
+        _check(self.lib.ctapp_debug_queue_slots(int(num_tiles), int(tiles_n), int(src_group), _ptr(src_windows), nw, _ptr(out), device, _stream(device)))
+        return out.cpu()
 
     # ---- harness natives
     def enable_peer_access(self, dev, peer):
@@ -353,7 +384,8 @@ class Tp4Module:
 
     def tp4_down(self, A, W, D, raster, swizzle, mode, rank, world, epoch, tile_cnt_mc=0, tile_cnt=None, partials_mc=0, x_mc=0,
                  resid=None, rowss_mc=0, panel_cnt_mc=0, sms=0, epoch_dev=None, rowss_mc_base=0, rowss_stride=0, d_ptr=0,
-                 dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None, cta_pair=0):
+                 dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None, cta_pair=0,
+                 tile_log=None):
         A, W = _bf16_matrix(A, "A"), _bf16_matrix(W, "W")
         if mode not in (0, 7):
             raise RuntimeError(f"tp4_down: mode {mode} is not available in this build (0 | 7)")
@@ -368,17 +400,44 @@ class Tp4Module:
         a.dst_ptrs, a.dst_rows = _ptr_array(dst_ptrs), int(dst_rows)
         a.peer_tile_flags, a.panels_per_owner = _ptr_array(peer_tile_flags), int(panels_per_owner)
         a.sms, a.pdl_trigger, a.pdl, a.tail_cols = int(sms), int(pdl_trigger), int(pdl), int(tail_cols)
-        a.trace, a.status, a.cta_pair = _ptr(trace), _ptr(status), int(cta_pair)
+        a.trace, a.status, a.cta_pair, a.tile_log = _ptr(trace), _ptr(status), int(cta_pair), _ptr(tile_log)
         dev = A.device.index
         _check(self.lib.ctapp_tp_down(C.byref(a), dev, _stream(dev)))
 
+    @staticmethod
+    def _reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
+                     rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=1, swz=1, unit_ctr=0, unit_log=None, pdl_trigger=0,
+                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
+        """The owner reducer's argument block (``ctapp_tp_reduce_args``), shared by tp4_reduce, tp4_reduce_noalloc and the mode-8
+        consumer.  ``panels_per_owner`` is required: the flags are indexed with it, and a wrong value aliases the sources."""
+        if panels_per_owner <= 0:
+            raise RuntimeError("panels_per_owner is required (the value the tile flags and the inbox were allocated with)")
+        a = TpReduceArgs()
+        a.M, a.n1, a.rank, a.world, a.epoch, a.epoch_dev = int(M), int(n1), int(rank), int(world), int(epoch), _ptr(epoch_dev)
+        a.blocks, a.threads = int(blocks), int(threads)
+        a.tile_flags = _ptr(tile_flags)
+        a.inbox, a.peer_x = _ptr_array(inbox_ptrs), _ptr_array(peer_x)
+        a.peer_rowss, a.peer_panel_flag = _ptr_array(peer_rowss), _ptr_array(peer_panel_flag)
+        a.resid = _ptr(resid)
+        a.rowss_local, a.panel_done = _ptr(rowss_local), _ptr(panel_done)
+        a.panels_per_owner, a.tail_cols, a.order, a.swz = int(panels_per_owner), int(tail_cols), int(order), int(swz)
+        a.unit_ctr, a.unit_log, a.pdl_trigger = _ptr(unit_ctr), _ptr(unit_log), int(pdl_trigger)
+        a.trace, a.status = _ptr(red_trace), _ptr(status)
+        a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
+        return a
+
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
-                tile=256, trace=0, status=None, eps=1e-5, cta_pair=0, act=0, **unsupported):
-        """``act=1``: W is (2 I, K) with gate and up rows interleaved in blocks of 128 (``interleave_gate_up``) and Y is (M, I) =
-        silu(gate) * up; needs ``cta_pair``."""
+                tile=256, R=0, role_ctr=None, rank=0, red_order=1, red_swz=1, tile_flags=None, resid=None, inbox_ptrs=(), peer_x=(),
+                peer_rowss=(), peer_panel_flag=(), rowss_local=0, panel_done=0, panels_per_owner=0, red_rows=4, trace=0, red_trace=0,
+                red_stages=0, red_dyn=0, red_tail=0, status=None, eps=1e-5, cta_pair=0, act=0, world=1, unit_ctr=None,
+                x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
+        """Modes 0 (plain, optional row scaling), 5 (per-panel waits) and 8: as 5, and every CTA first helps the owner reducer by
+        claiming units from ``unit_ctr`` (default ``role_ctr[1:]``), for which the reducer's arguments (``rank`` .. ``red_tail``,
+        named as in the reference binding) are needed.  ``act=1``: W is (2 I, K) with gate and up rows interleaved in blocks of
+        128 (``interleave_gate_up``) and Y is (M, I) = silu(gate) * up; needs ``cta_pair``."""
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
-        if mode not in (0, 5):
-            raise RuntimeError(f"tp4_qkv: mode {mode} is not available in this build (0 | 5)")
+        if mode not in (0, 5, 8):
+            raise RuntimeError(f"tp4_qkv: mode {mode} is not available in this build (0 | 5 | 8)")
         a = TpQkvArgs()
         a.X, a.W, a.Y = _ptr(X), _ptr(W), _ptr(Y)
         a.M, a.K = X.shape
@@ -387,31 +446,35 @@ class Tp4Module:
             raise RuntimeError(f"shape mismatch X{tuple(X.shape)} W{tuple(W.shape)} Y{tuple(Y.shape)} act={act}")
         a.act = int(act)
         a.raster, a.swizzle, a.mode, a.epoch, a.epoch_dev = int(raster), int(swizzle), int(mode), int(epoch), _ptr(epoch_dev)
-        a.panel_flag = _ptr(panel_cnt) if mode == 5 else None
+        a.panel_flag = _ptr(panel_cnt) if mode in (5, 8) else None
         a.rowss = _ptr(rowss)
         a.eps, a.sms, a.pdl, a.tile = float(eps), int(sms), int(pdl), int(tile)
         a.trace, a.status, a.cta_pair = _ptr(trace), _ptr(status), int(cta_pair)
+        red = None
+        if mode == 8:
+            if unit_ctr is None:
+                unit_ctr = role_ctr[1:] if role_ctr is not None else None
+            red = self._reduce_args(a.M, rank, world, epoch, epoch_dev, 1, 32, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
+                                    rowss_local, panel_done, panels_per_owner, red_tail, a.K, status, order=red_order, swz=red_swz,
+                                    unit_ctr=unit_ctr, red_trace=red_trace, x_mc_ptr=x_mc_ptr, rowss_mc_ptr=rowss_mc_ptr,
+                                    panel_flag_mc_ptr=panel_flag_mc_ptr)
+            a.red = C.cast(C.pointer(red), C.c_void_p)
         dev = X.device.index
         _check(self.lib.ctapp_tp_qkv(C.byref(a), dev, _stream(dev)))
 
     def tp4_reduce(self, M, rank, world, epoch, raster, blocks, tile_cnt, partials_mc=0, x_mc=0, resid=None, rowss_mc=0, panel_cnt_mc=0,
                    unicast=0, peer_partials=(), peer_x=(), version=5, epoch_dev=None, inbox_ptrs=(), peer_rowss=(), peer_panel_flag=(),
                    rowss_local=0, panel_done=0, panels_per_owner=0, threads=1024, variant=1, swz=1, rows=2, red_trace=0, dsmem=0, stages=0,
-                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
+                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, unit_log=None):
+        """Owner reducer, protocol version 5 (``raster`` = the producer's tile order: 1 = m fastest, 2 = n fastest; ``swz`` = its
+        n-tile group size).  ``variant`` / ``rows`` / ``stages`` / ``dsmem`` of the reference select kernels that have one
+        counterpart here and are accepted without effect."""
         if version != 5:
             raise RuntimeError(f"tp4_reduce: version {version} is not available in this build (5)")
-        a = TpReduceArgs()
-        a.M, a.n1, a.rank, a.world, a.epoch, a.epoch_dev = int(M), int(n1), int(rank), int(world), int(epoch), _ptr(epoch_dev)
-        a.blocks, a.threads = int(blocks), int(threads)
-        a.tile_flags = _ptr(tile_cnt)
-        a.inbox, a.peer_x = _ptr_array(inbox_ptrs), _ptr_array(peer_x)
-        a.peer_rowss, a.peer_panel_flag = _ptr_array(peer_rowss), _ptr_array(peer_panel_flag)
-        a.resid = _ptr(resid)
-        a.rowss_local, a.panel_done = _ptr(rowss_local), _ptr(panel_done)
-        a.panels_per_owner, a.tail_cols = int(panels_per_owner), int(tail_cols)
-        a.unit_ctr, a.trace, a.status = _ptr(unit_ctr), _ptr(red_trace), _ptr(status)
-        a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
-        a.tma = 1 if variant == 3 else 0
+        a = self._reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_cnt, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
+                              rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=2 if raster == 2 else 1, swz=swz,
+                              unit_ctr=unit_ctr, unit_log=unit_log, pdl_trigger=pdl_trigger, red_trace=red_trace, x_mc_ptr=x_mc_ptr,
+                              rowss_mc_ptr=rowss_mc_ptr, panel_flag_mc_ptr=panel_flag_mc_ptr)
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
 
@@ -443,18 +506,13 @@ class Tp4Module:
         return r[0], r[1]
 
     def tp4_reduce_noalloc(self, M, rank, world, epoch, blocks, tile_flags, resid=None, peer_x=(), epoch_dev=None, inbox_ptrs=(),
-                           peer_rowss=(), peer_panel_flag=(), panels_per_owner=0, threads=1024, tail_cols=0, n1=8192, status=None):
+                           peer_rowss=(), peer_panel_flag=(), panels_per_owner=0, threads=1024, tail_cols=0, n1=8192, status=None, **refused):
         """The owner reducer without caller scratch buffers and without any allocation (``ctapp_tp_reduce_noalloc``): for hosts
         that may not allocate device memory while running.  M <= 16384; calls that overlap on the GPU race on the shared
-        built-in scratch; make the first call on a device outside stream capture."""
-        a = TpReduceArgs()
-        a.M, a.n1, a.rank, a.world, a.epoch, a.epoch_dev = int(M), int(n1), int(rank), int(world), int(epoch), _ptr(epoch_dev)
-        a.blocks, a.threads = int(blocks), int(threads)
-        a.tile_flags = _ptr(tile_flags)
-        a.inbox, a.peer_x = _ptr_array(inbox_ptrs), _ptr_array(peer_x)
-        a.peer_rowss, a.peer_panel_flag = _ptr_array(peer_rowss), _ptr_array(peer_panel_flag)
-        a.resid = _ptr(resid)
-        a.panels_per_owner, a.tail_cols, a.status = int(panels_per_owner), int(tail_cols), _ptr(status)
+        built-in scratch; make the first call on a device (or ``preload``) outside stream capture.  Multicast addresses, a unit
+        counter or a unit log (``x_mc_ptr`` ..., ``unit_ctr``, ``unit_log``) are passed on and refused by the library."""
+        a = self._reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
+                              0, 0, panels_per_owner, tail_cols, n1, status, **refused)
         dev = tile_flags.device.index
         _check(self.lib.ctapp_tp_reduce_noalloc(C.byref(a), dev, _stream(dev)))
 

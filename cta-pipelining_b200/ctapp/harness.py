@@ -50,16 +50,32 @@ def time_one_gpu(fn, dev, iters, warmup):
     return statistics.median(_event_ms(fn, dev) for _ in range(iters))
 
 
+def _quiesce(dev, side_group, seconds):
+    """Drain this rank's GPU, then meet the other ranks (bounded: a rank that is already gone must not hold the others)."""
+    import datetime
+    try:
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
+        if side_group is not None:
+            dist.monitored_barrier(group=side_group, timeout=datetime.timedelta(seconds=seconds))
+        return True
+    except BaseException:  # noqa: BLE001
+        return False
+
+
 def _worker(rank, world, port, fn, args, results, backend):
-    """Body of one spawned rank: join the groups, run ``fn``, report, and leave without tearing the groups down (a peer may
-    already be gone, and a teardown that waits for it would never return)."""
+    """Body of one spawned rank: join the groups, run ``fn``, report.  A rank leaves only with its GPU idle and its symmetric
+    buffers (which may be bound to an NVLink multicast object) released, and after having waited (bounded) for the other
+    ranks to be idle too: a peer may still be storing into this rank's memory while its own kernels finish.  The process
+    groups themselves are not torn down (a peer may already be gone, and a teardown that waits for it would never return)."""
+    import gc
     from ctapp import tp4
     os.environ.setdefault("TORCH_NCCL_ENABLE_MONITORING", "0")
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     pkg = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     if pkg not in sys.path:
         sys.path.insert(0, pkg)
-    status = 0
+    status, dev, report = 0, torch.device("cpu"), None
     try:
         url = f"tcp://127.0.0.1:{port}"
         if backend == "nccl":
@@ -68,27 +84,37 @@ def _worker(rank, world, port, fn, args, results, backend):
             dist.init_process_group("nccl", init_method=url, rank=rank, world_size=world, device_id=dev)
             tp4.GLOO = dist.new_group(backend="gloo")
         else:
-            dev = torch.device("cpu")
             dist.init_process_group("gloo", init_method=url, rank=rank, world_size=world)
             tp4.GLOO = dist.group.WORLD
         value = fn(rank, world, dev, dist.group.WORLD.group_name, *args)
         if backend == "nccl":
             torch.cuda.synchronize(dev)
         tp4.barrier()
-        results.put((rank, True, value))
+        report = (rank, True, value)
     except BaseException:  # noqa: BLE001
         traceback.print_exc()
-        results.put((rank, False, traceback.format_exc()))
+        report = (rank, False, traceback.format_exc())
         status = 1
+    results.put(report)
+    # leave in order: everybody idle -> drop the buffers (frames of a raised exception would keep them alive) -> idle again
+    side = tp4.GLOO if dist.is_initialized() else None
+    _quiesce(dev, side, 20.0)
+    sys.last_traceback = sys.last_value = None
+    gc.collect()
+    if dev.type == "cuda":
+        torch.cuda.empty_cache()
+    _quiesce(dev, side, 20.0)
     sys.stdout.flush(); sys.stderr.flush()
     results.close(); results.join_thread()
     os._exit(status)
 
 
-def launch(fn, world, port, *args, backend="nccl", grace_s=10.0):
+def launch(fn, world, port, *args, backend="nccl", grace_s=60.0):
     """Run ``fn(rank, world, dev, group_name, *args)`` in ``world`` spawned processes (one per GPU; backend "gloo" runs them on
     the CPU).  Returns (per-rank results, bad): a rank that raised or vanished leaves None and makes ``bad`` true.  Once a
-    rank has failed the others get ``grace_s`` seconds (they may be blocked in a collective with it) and are then stopped."""
+    rank has failed the others get ``grace_s`` seconds and are then stopped.  That is long enough for every device-side wait
+    to have given up (they are bounded at two seconds) and for the survivors' own exit sequence (GPU idle, buffers released),
+    so a rank is only ever stopped with no kernel of its own in flight."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -167,7 +167,7 @@ class Pipeline:
     one after the other on the same stream."""
 
     def __init__(self, M, K, N1, N2, cfg1, cfg2, devA=0, devB=1, skip_wait=0, fence=0, group_rows=0, scoreboard="rowpanel"):
-        assert scoreboard in ("rowpanel", "tile")
+        assert scoreboard in ("rowpanel", "tile", "kchunk")
         ch = Chain(M, K, [N1, N2], [devA, devB], cfg=[cfg1, cfg2], group_rows=group_rows, scoreboard=scoreboard,
                    fence=fence, skip_wait=skip_wait)
         self.chain, self.ext = ch, ch.ext
@@ -198,7 +198,13 @@ class Pipeline:
 class Chain:
     """N-stage chain driven from one process: stage g runs on ``devices[g]`` with weight W_g (N_g, N_{g-1}); its output
     tiles land in the memory of ``devices[g+1]`` and are announced in that GPU's work queue.  Repeated devices are
-    allowed (stages then run back to back on that GPU's stream)."""
+    allowed (stages then run back to back on that GPU's stream).
+
+    scoreboard: "rowpanel" / "tile" = the reference's dependency CSR + scoreboard + work queue (a consumer tile is released
+    when its whole row panel, or tile set, is complete).  "kchunk" = value flags per producer tile instead: every stage walks
+    its own fixed tile order (``group_rows`` for all of them) and a consuming tile waits, k-chunk by k-chunk, for the flag
+    of the producer tile that holds those columns of its input rows, so its main loop streams behind the producer while both
+    keep an L2-friendly order.  Needs tiles of the same height on both sides of every link."""
 
     def __init__(self, M, K, widths, devices, cfg=3, group_rows=8, scoreboard="rowpanel", fence=1, skip_wait=0, sms=0, stamps=False,
                  consumer_group="auto"):
@@ -210,6 +216,8 @@ class Chain:
         self.devs = [torch.device("cuda", d) for d in devices]
         assert len(self.devs) == len(self.widths) >= 1
         self.rowpanel = int(scoreboard == "rowpanel")
+        self.kchunk = scoreboard == "kchunk"
+        self.run_id = 0          # k-chunk flags carry the run's number: they only ever grow and are never reset
         for a, b in zip(devices[:-1], devices[1:]):
             if a != b:
                 self.ext.enable_peer_access(a, b); self.ext.enable_peer_access(b, a)
@@ -218,18 +226,24 @@ class Chain:
         tiles = [_tile(self.ext, c) for c in self.cfg]
         i32 = dict(dtype=torch.int32)
         L = len(self.widths)
-        wins = [0] + [consumer_window(group_rows, self.rowpanel, tiles[g - 1][0], tiles[g][0], -(-M // tiles[g][0])) if consumer_group == "auto"
-                      else consumer_group for g in range(1, L)]
+        wins = [0] + [0 if self.kchunk else consumer_window(group_rows, self.rowpanel, tiles[g - 1][0], tiles[g][0], -(-M // tiles[g][0]))
+                      if consumer_group == "auto" else consumer_group for g in range(1, L)]
+        if self.kchunk:
+            assert all(t[0] == tiles[0][0] for t in tiles), f"k-chunk dependencies need tiles of one height on every stage, got {tiles}"
         self.src_group, self.src_windows = zip(*[_window_args(w, self.devs[g]) for g, w in enumerate(wins)])
         self.tn = [-(-n // t[1]) for n, t in zip(self.widths, tiles)]
         self.ntiles = [-(-M // t[0]) * tn for t, tn in zip(tiles, self.tn)]
         self.entries, self.head, self.tail, self.Y, self.status = [], [], [], [], []
         self.dep_off, self.dep_cons, self.sb, self.sb_pristine = [], [], [], []
+        # k-chunk mode: chunk[g] = flags of stage g's INPUT rows, in stage g's memory, one per tile of stage g-1
+        self.chunk = [None] + [torch.zeros(-(-M // tiles[g][0]), self.tn[g - 1], device=self.devs[g], **i32) if self.kchunk else None
+                               for g in range(1, L)]
+        self.chunk_kblocks = [0] + [tiles[g - 1][1] // 64 for g in range(1, L)]
         for g in range(L):
             dev = self.devs[g]
-            if g == 0:
-                self.entries.append(producer_order(self.ntiles[0], self.tn[0], group_rows).to(dev))
-                self.tail.append(torch.full((1,), self.ntiles[0], device=dev, **i32))
+            if g == 0 or self.kchunk:
+                self.entries.append(producer_order(self.ntiles[g], self.tn[g], group_rows).to(dev))     # a fixed order, always full
+                self.tail.append(torch.full((1,), self.ntiles[g], device=dev, **i32))
             else:
                 self.entries.append(torch.full((self.ntiles[g],), EMPTY, device=dev, **i32))
                 self.tail.append(torch.zeros(1, device=dev, **i32))
@@ -239,7 +253,7 @@ class Chain:
                 self.stamps = (self.stamps or []) + [torch.zeros(256 * 8, dtype=torch.int64, device=dev)]
             out_dev = self.devs[g + 1] if g + 1 < L else dev
             self.Y.append(torch.empty(M, self.widths[g], device=out_dev, dtype=torch.bfloat16))
-            if g + 1 < L:
+            if g + 1 < L and not self.kchunk:
                 off, cons, sb = build_deps(M, self.widths[g], self.widths[g + 1], *tiles[g], *tiles[g + 1], bool(self.rowpanel))
                 self.dep_off.append(off.to(dev)); self.dep_cons.append(cons.to(dev))
                 self.sb_pristine.append(sb.to(dev)); self.sb.append(sb.to(dev).clone())
@@ -251,9 +265,10 @@ class Chain:
         stage g+1's memory only after that stage's reset, which a stream event orders across GPUs."""
         L = len(self.widths)
         evs = [None] * L
+        self.run_id += 1
         for g in range(L):
             with torch.cuda.device(self.devs[g]):
-                self.ext.chain_reset(None if g == 0 else self.entries[g], self.head[g], self.tail[g], self.sb[g], self.sb_pristine[g])
+                self.ext.chain_reset(None if g == 0 or self.kchunk else self.entries[g], self.head[g], self.tail[g], self.sb[g], self.sb_pristine[g])
                 if g > 0 and self.devs[g - 1] != self.devs[g]:
                     evs[g] = torch.cuda.Event(); evs[g].record()
         for g in range(L - 1):
@@ -266,12 +281,15 @@ class Chain:
             with torch.cuda.device(self.devs[g]):
                 inp = X if g == 0 else self.Y[g - 1]
                 last = g + 1 == L
+                queued = not last and not self.kchunk        # publish into the next stage's work queue
                 self.ext.ctapp_gemm(inp, Ws[g], self.Y[g], self.cfg[g], self.entries[g], self.head[g], self.tail[g],
                                     self.dep_off[g], self.dep_cons[g], self.sb[g],
-                                    None if last else self.entries[g + 1], None if last else self.head[g + 1],
-                                    None if last else self.tail[g + 1], self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
-                                    tiles_n2=0 if last else self.tn[g + 1], rowpanel=self.rowpanel, status=self.status[g], sms=self.sms,
-                                    stamps=self.stamps[g] if self.stamps else None, src_group=self.src_group[g], src_windows=self.src_windows[g])
+                                    self.entries[g + 1] if queued else None, self.head[g + 1] if queued else None,
+                                    self.tail[g + 1] if queued else None, self.tn[g], self.skip_wait if g > 0 else 0, self.fence,
+                                    tiles_n2=self.tn[g + 1] if queued else 0, rowpanel=self.rowpanel, status=self.status[g], sms=self.sms,
+                                    stamps=self.stamps[g] if self.stamps else None, src_group=self.src_group[g], src_windows=self.src_windows[g],
+                                    chunk_dst=None if last else self.chunk[g + 1], chunk_src=self.chunk[g], chunk_kblocks=self.chunk_kblocks[g],
+                                    chunk_value=self.run_id)
         return self.Y[-1]
 
     def run(self, X, Ws):

@@ -75,6 +75,22 @@ class _Allocation:
             pass
 
 
+class _IpcMappings:
+    """This rank's allocation plus its mappings of the peers' copies; the mappings are closed before the allocation is freed.
+    Peers may still have this rank's copy mapped: callers drop their handles only after a barrier (the worker harness does)."""
+
+    def __init__(self, alloc, opened, device):
+        self.alloc, self.opened, self.device = alloc, opened, device
+
+    def __del__(self):
+        for p in self.opened:
+            try:
+                lib().ctapp_ipc_close(C.c_void_p(p), self.device)
+            except Exception:
+                pass
+        self.opened = []
+
+
 class LocalGroup:
     """All ranks live in this process: rank r uses ``devices[r]`` (devices may repeat; world 1 is one GPU talking to
     itself).  The k-th ``symm_empty`` call of every rank refers to the same logical buffer."""
@@ -127,8 +143,9 @@ def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
     if multicast or os.environ.get("CTAPP_SYMM", "ipc") == "torch":
         import torch.distributed._symmetric_memory as symm_mem
         t = symm_mem.empty(*_shape(shape), dtype=dtype, device=dev)
-        hdl = symm_mem.rendezvous(t, group if isinstance(group, str) else dist.group.WORLD.group_name)
         t.zero_()
+        torch.cuda.synchronize(dev)          # zeroed before any peer learns the address (the rendezvous is the barrier):
+        hdl = symm_mem.rendezvous(t, group if isinstance(group, str) else dist.group.WORLD.group_name)   # a late zero_ could erase a peer's flag
         return t, SymmHandle(list(hdl.buffer_ptrs), getattr(hdl, "multicast_ptr", 0) or 0, keep=(t, hdl))
     device = dev.index if isinstance(dev, torch.device) else int(dev)
     nbytes = _numel(shape) * torch.empty((), dtype=dtype).element_size()
@@ -151,4 +168,4 @@ def symm_empty(shape, dtype, dev, group, rank=None, multicast=False):
         _check(lib().ctapp_ipc_open(gathered[r], C.byref(p), device))
         ptrs.append(p.value)
         opened.append(p.value)
-    return t, SymmHandle(ptrs, 0, keep=(alloc, opened))
+    return t, SymmHandle(ptrs, 0, keep=_IpcMappings(alloc, opened, device))

@@ -1,57 +1,94 @@
-"""Gated latency measurement (mirrors reference ctapp/timing.py:10-35): every participating stream first blocks on a flag in
-pinned host memory (``cuStreamWaitValue32``), the work is enqueued behind it, and the gate is opened once everything is
-queued, so host launch cost stays outside the timed window."""
+"""Gated latency measurement (the role of reference ctapp/timing.py:10-35).
+
+A run is timed from the moment the GPUs are let loose to the moment the last of them is done, with the host's launch cost
+kept out of the window: while the ``Gate`` is closed every participating stream sits on a ``cuStreamWaitValue32`` of a word
+in pinned host memory, the work is queued up behind those waits, and opening the gate releases all streams at once.
+``measure`` keeps the reference's signature: ``method.prepare()`` (untimed), ``method.enqueue()`` (timed)."""
 from __future__ import annotations
 
+import contextlib
 import statistics
 
 import torch
 
 from ctapp.ext import load
 
-ext = None
+
+class Gate:
+    """The pinned host word all streams wait on.  ``with gate.closed(streams): ...`` queues a wait on every stream, runs the body
+    (which enqueues the work to be released), and opens the gate on exit."""
+
+    _ext = None
+
+    def __init__(self):
+        if Gate._ext is None:
+            Gate._ext = load()
+            Gate._ext.gate_alloc()
+        self.ext = Gate._ext
+
+    @contextlib.contextmanager
+    def closed(self, streams):
+        self.ext.gate_set(0)
+        for s in streams:
+            with torch.cuda.device(s.device), torch.cuda.stream(s):
+                self.ext.gate_wait()
+        try:
+            yield self
+        finally:
+            self.ext.gate_set(1)
 
 
-def _ext():
-    global ext
-    if ext is None:
-        ext = load()
-        ext.gate_alloc()
-    return ext
+class _Span:
+    """Start / stop events on the first stream; ``stop`` first makes that stream wait for everything queued on the others."""
+
+    def __init__(self, streams):
+        self.streams = streams
+        self.lead = streams[0]
+        self.t0 = torch.cuda.Event(enable_timing=True)
+        self.t1 = torch.cuda.Event(enable_timing=True)
+
+    def start(self):
+        with torch.cuda.device(self.lead.device):
+            self.t0.record(self.lead)
+
+    def stop(self):
+        for s in self.streams[1:]:
+            with torch.cuda.device(s.device):
+                done = torch.cuda.Event()
+                done.record(s)
+            self.lead.wait_event(done)
+        with torch.cuda.device(self.lead.device):
+            self.t1.record(self.lead)
+
+    def microseconds(self):
+        for s in self.streams:
+            s.synchronize()
+        return self.t0.elapsed_time(self.t1) * 1e3
+
+
+def gated_run(gate, streams, prepare, enqueue):
+    """One gated run -> device time in microseconds between the gate opening and the last stream finishing."""
+    prepare()
+    span = _Span(streams)
+    with gate.closed(streams):
+        span.start()         # queued behind the gate on the lead stream: fires when the gate opens
+        enqueue()
+        span.stop()
+    return span.microseconds()
 
 
 def measure(method, reps=20, warmup=5, devs=(0, 1), times=None):
-    """``method.prepare()`` runs before the gate closes; ``method.enqueue()`` is what is timed.  Returns (median, p10, p90) in
-    microseconds, measured with CUDA events on ``devs[0]``'s stream, which waits for every other device's last work."""
-    e = _ext()
+    """(median, 10th percentile, 90th percentile) in microseconds over ``reps`` gated runs of ``method`` on the current streams
+    of ``devs`` (the events live on ``devs[0]``).  One ungated run comes first, so that nothing has to be loaded or allocated
+    while the streams are blocked."""
+    gate = Gate()
     streams = [torch.cuda.current_stream(d) for d in devs]
-    # one ungated run first: nothing may have to be loaded or allocated while the streams are blocked
-    method.prepare(); method.enqueue()
-    for d in devs:
-        torch.cuda.synchronize(d)
-    ts = []
-    for i in range(warmup + reps):
-        method.prepare()
-        e.gate_set(0)
-        for d, s in zip(devs, streams):
-            with torch.cuda.device(d), torch.cuda.stream(s):
-                e.gate_wait()
-        with torch.cuda.device(devs[0]):
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record(streams[0])
-        method.enqueue()
-        for d, s in zip(devs[1:], streams[1:]):
-            with torch.cuda.device(d):
-                ev = torch.cuda.Event(); ev.record(s)
-            streams[0].wait_event(ev)
-        with torch.cuda.device(devs[0]):
-            end.record(streams[0])
-        e.gate_set(1)
-        for d in devs:
-            torch.cuda.synchronize(d)
-        if i >= warmup:
-            ts.append(start.elapsed_time(end) * 1e3)
+    method.prepare()
+    method.enqueue()
+    for s in streams:
+        s.synchronize()
+    samples = [gated_run(gate, streams, method.prepare, method.enqueue) for _ in range(warmup + reps)][warmup:]
     if times is not None:
-        times.extend(ts)
-    q = statistics.quantiles(ts, n=10, method="inclusive")
-    return statistics.median(ts), q[0], q[-1]
+        times.extend(samples)
+    deciles = statistics.quantiles(samples, n=10, method="inclusive")
+    return statistics.median(samples), deciles[0], deciles[-1]

@@ -69,14 +69,119 @@ def interleave_gate_up(W, block=128):
 
 
 # --------------------------------------------------------------------------- CTA-pipelined boundary
+FUSIONS = ("none", "pdl", "pdl1", "serial")
+
+# Symmetric buffers of one boundary instance: name -> (shape as a function of the sizes, dtype, wants a multicast address).
+# ``t`` = ranks, ``ppo`` = panels per owner, ``tn`` = 256-column tiles of the hidden size, ``P`` = max_M / 128.
+_SYMMETRIC = (
+    ("inbox", lambda z: (z.t, z.ppo * 128, z.n1), DTYPE, False),        # slot s = partial tiles from source rank s
+    ("tile_flags", lambda z: (z.t, z.ppo, z.tn), torch.int32, False),   # [source][owned panel][n-tile], epoch values
+    ("panel_flag", lambda z: (z.P,), torch.int32, True),                # epoch values, raised by the owners
+    ("rowss", lambda z: (2, z.max_M), torch.float32, True),             # row sums of squares, by epoch parity
+    ("xbuf", lambda z: (z.max_M, z.n1), DTYPE, True),                   # new residual stream, even epochs
+    ("xbuf1", lambda z: (z.max_M, z.n1), DTYPE, True),                  # ... odd epochs
+)
+
+
+class _Sizes:
+    def __init__(self, max_M, n1, world):
+        self.max_M, self.n1, self.t = max_M, n1, world
+        self.P, self.tn = max_M // 128, n1 // 256
+        self.ppo = -(-self.P // world)
+
+
+class _Buffers:
+    """Everything a boundary instance keeps on its GPU: the symmetric buffers of ``_SYMMETRIC`` (tensor + handle each), the
+    per-rank scratch, and the address tables the kernels take, derived from the handles."""
+
+    def __init__(self, sizes, dev, group, rank, want_multicast):
+        self.z, self.dev, self.rank = sizes, dev, rank
+        self.handles = {}
+        for name, shape, dtype, mc in _SYMMETRIC:
+            t, h = _symm(shape(sizes), dtype, dev, group, rank, mc and want_multicast)
+            setattr(self, name, t)
+            self.handles[name] = h
+        self.multicast = want_multicast and all(self.handles[n].multicast_ptr for n, _, _, mc in _SYMMETRIC if mc)
+        z = sizes
+        self.rowss_local = torch.zeros(z.max_M, dtype=torch.float32, device=dev)      # owner's accumulators, zeroed per step
+        self.panel_done = torch.zeros(z.P, dtype=torch.int32, device=dev)             # arrivals per owned panel
+        self.role_ctr = torch.zeros(2, dtype=torch.int32, device=dev)                 # [1] = the shared unit counter (steal)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = new_status(dev)
+        for t in (self.tile_flags, self.panel_flag, self.rowss):
+            t.zero_()
+
+    def peers(self, name, byte_offset=0):
+        return [p + byte_offset for p in self.handles[name].buffer_ptrs]
+
+    def mc(self, name, byte_offset=0):
+        return self.handles[name].multicast_ptr + byte_offset if self.multicast else 0
+
+    def tables(self):
+        """Address tables: where this rank's producer stores at every owner, where its reducer reads and pushes."""
+        z, slot = self.z, self.z.ppo * 128 * self.z.n1 * 2
+        return dict(
+            dst_ptrs=self.peers("inbox", self.rank * slot),                               # my slot in every owner's inbox
+            peer_tf=self.peers("tile_flags"),
+            inbox_local=[self.inbox.data_ptr() + s * slot for s in range(z.t)],
+            peer_x=[self.peers("xbuf"), self.peers("xbuf1")],
+            peer_rowss=[self.peers("rowss", par * z.max_M * 4) for par in (0, 1)],
+            peer_pf=self.peers("panel_flag"),
+            x_mc=[self.mc("xbuf"), self.mc("xbuf1")],
+            rowss_mc=[self.mc("rowss", par * z.max_M * 4) for par in (0, 1)],
+            pf_mc=self.mc("panel_flag"))
+
+
+class _GraphCache:
+    """CUDA graphs of a forward, one per key.  The first call of an instance runs eagerly (capture must not be the first
+    thing a context does with these kernels); from then on a key is captured the first time it is seen and replayed."""
+
+    def __init__(self, dev):
+        self.dev, self.graphs, self.primed = dev, {}, False
+
+    def run(self, key, enqueue):
+        if not self.primed:
+            self.primed = True
+            enqueue()
+            return
+        g = self.graphs.get(key)
+        if g is None:
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                enqueue()
+            self.graphs[key] = g
+        g.replay()
+
+
+def _check_options(world, protocol, fusion, steal, qkv_tile, down_tail, n1, act, cta_pair, N2r, M, max_M):
+    if world not in (1, 2, 4, 8):
+        raise ValueError(f"world {world} is not supported (1 | 2 | 4 | 8)")
+    if protocol not in (True, False, "v3", "v5"):
+        raise ValueError(f"unknown protocol {protocol!r}")
+    if fusion == "role":
+        raise ValueError("fusion='role' (the first R consumer CTAs ARE the reducer) is not built; steal=True gives every consumer CTA the "
+                         "reducer's claim loop, which covers it")
+    if fusion not in FUSIONS:
+        raise ValueError(f"fusion {fusion!r} is not available (none | pdl | pdl1 | serial)")
+    if qkv_tile not in (256, 128):
+        raise ValueError(f"qkv_tile {qkv_tile}")
+    if not (down_tail == "auto" or (isinstance(down_tail, int) and 0 <= down_tail <= n1 // 256)):
+        raise ValueError(f"down_tail {down_tail!r}")
+    if M % 128 or n1 % 256 or max_M % 128 or M > max_M:
+        raise ValueError(f"M={M} / max_M={max_M} must be multiples of 128 with M <= max_M, n1={n1} a multiple of 256")
+    if act and not (cta_pair and qkv_tile == 256 and N2r % 256 == 0):
+        raise ValueError("act needs the CTA-pair consumer and N2r % 256 == 0")
+
+
 class CtappBoundary:
     """CTA-pipelined boundary, panel-ownership protocol with unicast value flags (the reference's protocol "v5",
     ctapp/tp4.py:60-504), for world in {1, 2, 4, 8}.
 
     Per forward: ``tp4_step`` (epoch += 1, zero the per-step accumulators) -> producer GEMM mode 7 on ``SMs - R`` SMs ||
-    owner reducer (``red_blocks`` CTAs of ``red_threads`` threads on a second stream) -> consumer GEMM mode 5 on
-    ``SMs - R`` SMs.  All flags are epoch values, so one instance sized ``max_M`` serves every M <= max_M with
-    M % 128 == 0; ``out`` and ``x()`` are views of the first M rows.
+    owner reducer (``red_blocks`` CTAs of ``red_threads`` threads) -> consumer GEMM mode 5 / 8 on ``SMs - R`` SMs.  All flags
+    are epoch values, so one instance sized ``max_M`` serves every M <= max_M with M % 128 == 0; ``out`` and ``x()`` are
+    views of the first M rows.
 
     protocol: "v5" (default here) = unicast pushes; True / "v3" = NVLS variant: the same panel-ownership protocol, but the owner
     reducer pushes x, the row sums and the panel flags with ``multimem.st`` on multicast addresses, so each row leaves the
@@ -86,8 +191,15 @@ class CtappBoundary:
     fusion: "none" = reducer on a side stream, consumer after the producer in stream order;
             "pdl"  = as "none" and the consumer is launched as the producer's programmatic dependent, so its CTAs start
                      as producer CTAs retire (the per-panel flags carry the data dependency);
+            "pdl1" = one stream: reducer (raises the launch trigger at entry) -> producer -> consumer, each the programmatic
+                     dependent of the one before (reference ctapp/tp4.py:316-320);
             "serial" = step, producer, reducer, consumer on one stream, nothing concurrent on this GPU (used where a
                      single GPU plays every rank).
+    steal: the consumer runs in mode 8: each of its CTAs first claims owner-reducer units from the counter the dedicated
+    reducer CTAs claim from, so CTAs that become resident as the producer's retire drain what the reducer has not reached
+    (reference ctapp/tp4.py:110-114, csrc/ctapp_tp4.cuh:913-925).  ``R=0`` with steal leaves the reduction to them alone
+    (with fusion "serial" that only works for world 1: a consumer that reduces its own panels and then waits for the other
+    ranks' panels needs those ranks' consumers to run at the same time).
     use_graph: forwards are captured into CUDA graphs keyed by (parity, M); inputs are copied into static buffers
     before each replay (``graph_bind`` captures the caller's tensors instead).
     act: the consumer's weight is a gate/up projection with rows interleaved by ``interleave_gate_up``; its epilogue applies
@@ -102,245 +214,248 @@ class CtappBoundary:
                  qkv_raster=2, qkv_swizzle=1, max_M=None, down_raster=None, red_threads=1024, red_blocks=None, red_variant=1,
                  fusion="none", qkv_tile=256, role_rows=4, down_swizzle=1, pdl_trigger=None, trace=None, role_stages=0, steal=False,
                  down_tail="auto", graph_bind=False, n1=N1, eps=EPS, cta_pair=True, act=False):
-        assert M % 128 == 0 and n1 % 256 == 0, (M, n1)
-        assert not act or (cta_pair and qkv_tile == 256 and N2r % 256 == 0), "act needs the CTA-pair consumer and N2r % 256 == 0"
-        self.act = int(bool(act))
-        assert protocol in (True, False, "v3", "v5"), protocol
-        assert world in (1, 2, 4, 8), f"world {world} is not supported"
-        # True / "v3": NVLS variant -- the owner reducer pushes x, row sums and panel flags with multimem stores on multicast
-        # addresses (replicated inside the NVSwitch); needs one process per GPU, world >= 2 and multicast support
-        self.nvls = protocol in (True, "v3") and world >= 2 and not isinstance(group_name, LocalGroup)
-        if protocol in (True, "v3") and not self.nvls:
-            log.warning("ctapp: NVLS needs one process per GPU and at least 2 ranks; using unicast pushes")
-        assert fusion in ("none", "pdl", "serial"), f"fusion {fusion!r} is not available in this build (none | pdl | serial)"
-        assert red_variant in (1, 3), "reducer variants of this build: 1 = warp per unit (register loads), 3 = TMA-fed"
-        assert qkv_tile in (256, 128)
-        assert down_tail == "auto" or (isinstance(down_tail, int) and 0 <= down_tail <= n1 // 256), down_tail
+        max_M = max_M or M
+        _check_options(world, protocol, fusion, steal, qkv_tile, down_tail, n1, act, cta_pair, N2r, M, max_M)
         self.ext = load_tp4()
-        self.M, self.Kr, self.N2r, self.rank, self.world = M, Kr, N2r, rank, world
-        self.n1, self.eps, self.cta_pair = n1, eps, int(bool(cta_pair))
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
-        self.use_resid, self.protocol, self.use_graph, self.v5 = resid, bool(protocol), use_graph, bool(protocol)
-        self.group = group_name
-        self.R = R or (8 if world >= 4 else 4)   # measured on B200 at M=4096: TP2 best with 4, TP4 and TP8 with 8
-        self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
+        self.M, self.max_M, self.Kr, self.N2r, self.rank, self.world, self.group = M, max_M, Kr, N2r, rank, world, group_name
+        self.n1, self.eps, self.cta_pair, self.act = n1, eps, int(bool(cta_pair)), int(bool(act))
+        self.use_resid, self.protocol, self.v5 = resid, bool(protocol), bool(protocol)
+        self.use_graph, self.graph_bind = use_graph, bool(graph_bind)
+        self.fusion, self.steal = fusion, bool(steal)
+        # SM split: R SMs are left to the owner reducer (measured on B200 at M=4096: TP2 best with 4, TP4 and TP8 with 8)
         self.nsm = torch.cuda.get_device_properties(self.dev).multi_processor_count
-        self.sms = self.nsm - self.R
-        self.qkv_sms = self.sms
-        self.fusion, self.down_swizzle, self.down_tail, self.steal = fusion, down_swizzle, down_tail, bool(steal)
-        self.down_raster = down_raster or 1
-        self.red_threads, self.red_blocks, self.red_variant = red_threads, red_blocks or self.R, red_variant
-        self.graph_bind = bool(graph_bind)
-        self.pdl_trigger = (1 if fusion == "pdl" else 0) if pdl_trigger is None else int(pdl_trigger)
+        self.R = (8 if world >= 4 else 4) if R is None else int(R)
+        if self.R == 0 and not self.steal:
+            raise ValueError("R=0 (no dedicated reducer CTAs) needs steal=True")
+        self.sms = self.qkv_sms = self.nsm - self.R
+        self.red_threads, self.red_blocks = red_threads, red_blocks or self.R
+        # tile orders of the three kernels
+        self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
+        self.down_raster, self.down_swizzle, self.down_tail = down_raster or 1, down_swizzle, down_tail
+        self.pdl_trigger = int(fusion in ("pdl", "pdl1")) if pdl_trigger is None else int(pdl_trigger)
         self.trace = bool(int(os.environ.get("CTAPP_TRACE", "0"))) if trace is None else bool(trace)
-        self.max_M = max_M = max_M or M
-        assert max_M % 128 == 0 and M <= max_M, (M, max_M)
-        dev, tn = self.dev, n1 // 256
-        with torch.cuda.device(dev):
-            self.ext.preload(dev.index)
-            self.ppo = ppo = -(-(max_M // 128) // world)            # panels per owner (ceil)
-            sy = lambda shape, dt, mc=False: _symm(shape, dt, dev, group_name, rank, mc and self.nvls)  # noqa: E731
-            self.inbox, hi = sy((world, ppo * 128, n1), DTYPE)       # this rank's inbox; slot s = source rank s
-            self.tile_flags, ht = sy((world, ppo, tn), torch.int32)
-            self.panel_flag, hp = sy((max_M // 128,), torch.int32, True)
-            self.rowss, hr = sy((2, max_M), torch.float32, True)     # by epoch parity
-            self.xbuf, hx0 = sy((max_M, n1), DTYPE, True)
-            self.xbuf1, hx1 = sy((max_M, n1), DTYPE, True)
-            if self.nvls and not (hp.multicast_ptr and hr.multicast_ptr and hx0.multicast_ptr and hx1.multicast_ptr):
+        want_mc = protocol in (True, "v3") and world >= 2 and not isinstance(group_name, LocalGroup)
+        if protocol in (True, "v3") and not want_mc:
+            log.warning("ctapp: NVLS needs one process per GPU and at least 2 ranks; using unicast pushes")
+        sizes = _Sizes(max_M, n1, world)
+        with torch.cuda.device(self.dev):
+            self.ext.preload(self.dev.index)
+            self.buf = _Buffers(sizes, self.dev, group_name, rank, want_mc)
+            if want_mc and not self.buf.multicast:
                 log.warning("ctapp: no multicast address on this system; using unicast pushes")
-                self.nvls = False
-            self._x_mc = [hx0.multicast_ptr, hx1.multicast_ptr] if self.nvls else [0, 0]
-            self._rowss_mc = [hr.multicast_ptr + par * max_M * 4 for par in (0, 1)] if self.nvls else [0, 0]
-            self._pf_mc = hp.multicast_ptr if self.nvls else 0
-            self._hdls = (hi, ht, hp, hr, hx0, hx1)
-            self.xbufs = [self.xbuf, self.xbuf1]
-            slot = ppo * 128 * n1 * 2                                 # bytes of one inbox slot
-            self._dst_ptrs = [hi.buffer_ptrs[d] + rank * slot for d in range(world)]       # producer: my slot at every owner
-            self._peer_tf = [ht.buffer_ptrs[d] for d in range(world)]
-            self._inbox_local = [self.inbox.data_ptr() + s * slot for s in range(world)]   # reducer: my inbox, per source
-            self._peer_x = [[hx0.buffer_ptrs[d] for d in range(world)], [hx1.buffer_ptrs[d] for d in range(world)]]
-            self._peer_rowss = [[hr.buffer_ptrs[d] + par * max_M * 4 for d in range(world)] for par in (0, 1)]
-            self._peer_pf = [hp.buffer_ptrs[d] for d in range(world)]
-            self.rowss_local = torch.zeros(max_M, dtype=torch.float32, device=dev)
-            self.panel_done = torch.zeros(max_M // 128, dtype=torch.int32, device=dev)
-            self.role_ctr = torch.zeros(2, dtype=torch.int32, device=dev)
-            self.status = new_status(dev)
-            self.trace_down = torch.zeros(self.nsm * 8, dtype=torch.int64, device=dev)
-            self.trace_qkv = torch.zeros(self.nsm * 8, dtype=torch.int64, device=dev)
-            self.trace_red = torch.zeros(max_M // 128, dtype=torch.int64, device=dev)
-            for t in (self.tile_flags, self.panel_flag, self.rowss):
-                t.zero_()
-            self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
-            self.s_red = torch.cuda.Stream(device=dev)
-            self.ev_start, self.ev_red = torch.cuda.Event(), torch.cuda.Event()
-            torch.cuda.synchronize(dev)
-            self._out_full = torch.empty(max_M, N2r // 2 if self.act else N2r, dtype=DTYPE, device=dev)
+            self.nvls = self.buf.multicast
+            self.tab = self.buf.tables()
+            self.trace_down = torch.zeros(self.nsm * 8, dtype=torch.int64, device=self.dev)
+            self.trace_qkv = torch.zeros(self.nsm * 8, dtype=torch.int64, device=self.dev)
+            self.trace_red = torch.zeros(sizes.P, dtype=torch.int64, device=self.dev)
+            self.side = torch.cuda.Stream(device=self.dev)
+            self.fork, self.join = torch.cuda.Event(), torch.cuda.Event()
+            self._out_full = torch.empty(max_M, N2r // 2 if self.act else N2r, dtype=DTYPE, device=self.dev)
             self._floor_y = None
-            self.h_static = torch.empty(max_M, Kr, dtype=DTYPE, device=dev) if use_graph and not graph_bind else None
-            self.resid_static = torch.empty(max_M, n1, dtype=DTYPE, device=dev) if use_graph and resid and not graph_bind else None
+            static = use_graph and not self.graph_bind
+            self.h_static = torch.empty(max_M, Kr, dtype=DTYPE, device=self.dev) if static else None
+            self.resid_static = torch.empty(max_M, n1, dtype=DTYPE, device=self.dev) if static and resid else None
+            torch.cuda.synchronize(self.dev)
         _group_barrier(group_name)
+        self.ppo = sizes.ppo
         self.out = self._out_full[:M]
         self.epoch = 0
-        self._last_par, self._last_M = 0, M
+        self._last = (0, M)          # (parity, M) of the most recent forward
         self.Wd = self.Wq = None
-        self._graphs = {}
-        self._warm = False
-        self._warmed = True     # kernels are loaded by preload(); no warm-up launches are needed
+        self._graphs = _GraphCache(self.dev)
+        self._enqueue = {"serial": self._enqueue_serial, "none": self._enqueue_forked, "pdl": self._enqueue_forked,
+                         "pdl1": self._enqueue_chained}[fusion]
 
-    # ---- pieces of one forward
-    def _tail(self, M):
+    # the buffers tests and benches look at, by their reference names
+    inbox = property(lambda self: self.buf.inbox)
+    tile_flags = property(lambda self: self.buf.tile_flags)
+    panel_flag = property(lambda self: self.buf.panel_flag)
+    rowss = property(lambda self: self.buf.rowss)
+    xbuf = property(lambda self: self.buf.xbuf)
+    xbuf1 = property(lambda self: self.buf.xbuf1)
+    xbufs = property(lambda self: (self.buf.xbuf, self.buf.xbuf1))
+    rowss_local = property(lambda self: self.buf.rowss_local)
+    panel_done = property(lambda self: self.buf.panel_done)
+    role_ctr = property(lambda self: self.buf.role_ctr)
+    epoch_dev = property(lambda self: self.buf.epoch_dev)
+    status = property(lambda self: self.buf.status)
+
+    # ---- the three kernels of a step
+    def tail_cols(self, M):
+        """n-tiles the producer leaves for its panel-major tail (reference ctapp/tp4.py:262-267)."""
         if self.down_tail != "auto":
             return self.down_tail
-        if self.down_raster != 1 or self.down_swizzle != 1:
+        if (self.down_raster, self.down_swizzle) != (1, 1):
             return 0
-        return min(16 if M // 128 >= 16 else 8, self.n1 // 256)
+        return min(16 if M >= 2048 else 8, self.n1 // 256)
 
-    def _tr(self, t):
+    def _stamps(self, t):
         return t.data_ptr() if self.trace else 0
 
-    def _reduce_v5(self, M, resid, parity):
-        self.ext.tp4_reduce(M, self.rank, self.world, 0, self.down_raster, self.red_blocks, self.tile_flags, resid=resid,
-                            peer_x=self._peer_x[parity], version=5, epoch_dev=self.epoch_dev, inbox_ptrs=self._inbox_local,
-                            peer_rowss=self._peer_rowss[parity], peer_panel_flag=self._peer_pf, rowss_local=self.rowss_local,
-                            panel_done=self.panel_done, panels_per_owner=self.ppo, threads=self.red_threads, variant=self.red_variant,
-                            red_trace=self._tr(self.trace_red), unit_ctr=self.role_ctr[1:] if self.steal else 0,
-                            tail_cols=self._tail(M), n1=self.n1, status=self.status, x_mc_ptr=self._x_mc[parity],
-                            rowss_mc_ptr=self._rowss_mc[parity], panel_flag_mc_ptr=self._pf_mc)
+    def _reducer_kwargs(self, M, resid, parity):
+        """What the owner reducer needs, under the names both ``tp4_reduce`` and the mode-8 ``tp4_qkv`` take."""
+        t = self.tab
+        return dict(resid=resid, inbox_ptrs=t["inbox_local"], peer_x=t["peer_x"][parity], peer_rowss=t["peer_rowss"][parity],
+                    peer_panel_flag=t["peer_pf"], rowss_local=self.buf.rowss_local, panel_done=self.buf.panel_done,
+                    panels_per_owner=self.ppo, x_mc_ptr=t["x_mc"][parity], rowss_mc_ptr=t["rowss_mc"][parity],
+                    panel_flag_mc_ptr=t["pf_mc"], red_trace=self._stamps(self.trace_red), status=self.buf.status)
 
-    def _down_v5(self, h_r, Wd, M):
-        self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms,
-                          epoch_dev=self.epoch_dev, dst_ptrs=self._dst_ptrs, dst_rows=self.ppo * 128, peer_tile_flags=self._peer_tf,
-                          panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, trace=self._tr(self.trace_down),
-                          tail_cols=self._tail(M), status=self.status, cta_pair=self.cta_pair)
-
-    def _qkv_v5(self, Wq, M, parity):
-        self.ext.tp4_qkv(self.xbufs[parity][:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 5, 0, self.panel_flag, 1,
-                         self.rowss[parity], sms=self.qkv_sms, pdl=1 if self.fusion == "pdl" else 0, epoch_dev=self.epoch_dev,
-                         tile=self.qkv_tile, trace=self._tr(self.trace_qkv), status=self.status, eps=self.eps, cta_pair=self.cta_pair, act=self.act)
-
-    def _enqueue_v5(self, h_r, resid, parity, Wd, Wq, M):
-        cur = torch.cuda.current_stream(self.dev)
-        self.ext.tp4_step(self.epoch_dev, self.rowss_local, self.panel_done, M, self.role_ctr)
-        if self.fusion == "serial":
-            self._down_v5(h_r, Wd, M)
-            self._reduce_v5(M, resid, parity)
-            self._qkv_v5(Wq, M, parity)
+    def launch_reducer(self, M, resid, parity, unit_log=None):
+        if self.red_blocks == 0:
             return
-        self.ev_start.record(cur)
-        self.s_red.wait_event(self.ev_start)
-        with torch.cuda.stream(self.s_red):
-            self._reduce_v5(M, resid, parity)
-            self.ev_red.record(self.s_red)
-        self._down_v5(h_r, Wd, M)
-        self._qkv_v5(Wq, M, parity)
-        cur.wait_event(self.ev_red)
+        self.ext.tp4_reduce(M, self.rank, self.world, 0, self.down_raster, self.red_blocks, self.buf.tile_flags, version=5,
+                            epoch_dev=self.buf.epoch_dev, threads=self.red_threads, swz=self.down_swizzle, n1=self.n1,
+                            unit_ctr=self.buf.role_ctr[1:] if self.steal else 0, tail_cols=self.tail_cols(M),
+                            pdl_trigger=int(self.fusion == "pdl1"), unit_log=unit_log, **self._reducer_kwargs(M, resid, parity))
+
+    def launch_producer(self, h_r, Wd, M, tile_log=None, sms=None):
+        t = self.tab
+        self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms if sms is None else sms,
+                          epoch_dev=self.buf.epoch_dev, dst_ptrs=t["dst_ptrs"], dst_rows=self.ppo * 128, peer_tile_flags=t["peer_tf"],
+                          panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, pdl=int(self.fusion == "pdl1"),
+                          trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.cta_pair,
+                          tile_log=tile_log)
+
+    def launch_consumer(self, Wq, M, parity, resid=None):
+        common = dict(sms=self.qkv_sms, pdl=int(self.fusion in ("pdl", "pdl1")), epoch_dev=self.buf.epoch_dev, tile=self.qkv_tile,
+                      trace=self._stamps(self.trace_qkv), eps=self.eps, cta_pair=self.cta_pair, act=self.act)
+        args = (self.xbufs[parity][:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle)
+        if not self.steal:
+            self.ext.tp4_qkv(*args, 5, 0, self.buf.panel_flag, 1, self.buf.rowss[parity], status=self.buf.status, **common)
+            return
+        self.ext.tp4_qkv(*args, 8, 0, self.buf.panel_flag, 1, self.buf.rowss[parity], role_ctr=self.buf.role_ctr, rank=self.rank,
+                         world=self.world, red_order=2 if self.down_raster == 2 else 1, red_swz=self.down_swizzle,
+                         tile_flags=self.buf.tile_flags, red_tail=self.tail_cols(M), **self._reducer_kwargs(M, resid, parity), **common)
+
+    # ---- how the kernels of one step are put on streams
+    def _step(self, M):
+        self.ext.tp4_step(self.buf.epoch_dev, self.buf.rowss_local, self.buf.panel_done, M, self.buf.role_ctr)
+
+    def _enqueue_serial(self, h_r, resid, parity, Wd, Wq, M):
+        self._step(M)
+        self.launch_producer(h_r, Wd, M)
+        self.launch_reducer(M, resid, parity)
+        self.launch_consumer(Wq, M, parity, resid)
+
+    def _enqueue_forked(self, h_r, resid, parity, Wd, Wq, M):
+        """Reducer on the side stream, forked after the step kernel and joined after the consumer."""
+        main = torch.cuda.current_stream(self.dev)
+        self._step(M)
+        self.fork.record(main)
+        self.side.wait_event(self.fork)
+        with torch.cuda.stream(self.side):
+            self.launch_reducer(M, resid, parity)
+            self.join.record(self.side)
+        self.launch_producer(h_r, Wd, M)
+        self.launch_consumer(Wq, M, parity, resid)
+        main.wait_event(self.join)
+
+    def _enqueue_chained(self, h_r, resid, parity, Wd, Wq, M):
+        """One stream, three programmatic launches: the reducer lets the producer in at once, the producer the consumer."""
+        self._step(M)
+        self.launch_reducer(M, resid, parity)
+        self.launch_producer(h_r, Wd, M)
+        self.launch_consumer(Wq, M, parity, resid)
 
     def _enqueue_floor(self, h_r, Wd, Wq, M):
         """The two GEMMs with the same SM split and tile orders, no exchange (reference ctapp/tp4.py:365-369)."""
         if self._floor_y is None:
             self._floor_y = torch.empty(self.max_M, self.n1, dtype=DTYPE, device=self.dev)
         self.ext.tp4_down(h_r, Wd, self._floor_y[:M], self.down_raster, self.down_swizzle, 0, self.rank, self.world, 0, sms=self.sms,
-                          tail_cols=self._tail(M), cta_pair=self.cta_pair)
+                          tail_cols=self.tail_cols(M), cta_pair=self.cta_pair)
         self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile,
                          cta_pair=self.cta_pair, act=self.act)
 
     # ---- public API
     def warmup(self):
         """Kept for API compatibility: every kernel is loaded at construction (``ctapp_preload``), so nothing is launched."""
-        self._warmed = True
 
-    def _check_w(self, Wd, Wq):
-        assert Wd.shape == (self.n1, self.Kr) and Wd.dtype == DTYPE and Wd.is_contiguous(), (Wd.shape, Wd.dtype)
-        assert Wq.shape == (self.N2r, self.n1) and Wq.dtype == DTYPE and Wq.is_contiguous(), (Wq.shape, Wq.dtype)
+    def _weights(self, Wd, Wq):
+        Wd = self.Wd if Wd is None else Wd
+        Wq = self.Wq if Wq is None else Wq
+        if Wd is None or Wq is None:
+            raise ValueError("no weights: call set_weights() or pass Wd / Wq")
+        for w, shape, name in ((Wd, (self.n1, self.Kr), "Wd"), (Wq, (self.N2r, self.n1), "Wq")):
+            if tuple(w.shape) != shape or w.dtype != DTYPE or not w.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous bf16 {shape} tensor, got {tuple(w.shape)} {w.dtype}")
+        return Wd, Wq
 
     def set_weights(self, Wdown_r, Wqkv_r_folded):
         """Default weights (used when forward() gets none; baked into the graphs when use_graph)."""
-        self._check_w(Wdown_r, Wqkv_r_folded)
-        self.Wd, self.Wq = Wdown_r, Wqkv_r_folded
+        self.Wd, self.Wq = self._weights(Wdown_r, Wqkv_r_folded)
+
+    def _inputs(self, h_r, resid):
+        M = h_r.shape[0]
+        if M % 128 or not 0 < M <= self.max_M:
+            raise ValueError(f"M={M} must be a positive multiple of 128 up to max_M={self.max_M}")
+        for t, shape, name in ((h_r, (M, self.Kr), "h_r"), (resid, (M, self.n1), "resid")):
+            if t is not None and (tuple(t.shape) != shape or t.dtype != DTYPE or not t.is_contiguous()):
+                raise ValueError(f"{name} must be a contiguous bf16 {shape} tensor, got {tuple(t.shape)} {t.dtype}")
+        return M
 
     def forward(self, h_r, resid=None, Wd=None, Wq=None):
         """Wd (n1, Kr) / Wq (N2r, n1, gamma folded): bf16 contiguous weights for this call (no copy; they must stay alive
-        until the stream work finishes); default = those from set_weights.  Not supported with use_graph."""
-        if self.use_graph:
-            assert Wd is None and Wq is None, "per-call weights are not supported with use_graph"
-        Wd = self.Wd if Wd is None else Wd
-        Wq = self.Wq if Wq is None else Wq
-        assert Wd is not None and Wq is not None, "no weights: call set_weights() or pass Wd/Wq"
-        self._check_w(Wd, Wq)
-        r = resid if self.use_resid else None
-        M = h_r.shape[0]
-        assert M % 128 == 0 and 0 < M <= self.max_M, (M, self.max_M)
-        assert h_r.shape == (M, self.Kr) and h_r.dtype == DTYPE and h_r.is_contiguous(), (h_r.shape, h_r.dtype)
-        if r is not None:
-            assert r.shape == (M, self.n1) and r.dtype == DTYPE and r.is_contiguous(), (r.shape, r.dtype)
+        until the stream work finishes); default = those from set_weights.  Per-call weights are not supported with use_graph."""
+        if self.use_graph and not (Wd is None and Wq is None):
+            raise ValueError("per-call weights are not supported with use_graph")
+        Wd, Wq = self._weights(Wd, Wq)
+        resid = resid if self.use_resid else None
+        M = self._inputs(h_r, resid)
         self.out = self._out_full[:M]
-        self._last_M = M
         with torch.cuda.device(self.dev):
             if not self.protocol:
+                self._last = (0, M)
                 self._enqueue_floor(h_r, Wd, Wq, M)
                 return self.out
             self.epoch += 1
-            par = self.epoch & 1
-            self._last_par = par
-            if r is not None:
-                assert r.data_ptr() != self.xbufs[par].data_ptr(), "resid aliases the x buffer written by this forward"
+            parity = self.epoch & 1
+            self._last = (parity, M)
+            if resid is not None and resid.data_ptr() == self.xbufs[parity].data_ptr():
+                raise ValueError("resid aliases the x buffer this forward writes")
             if not self.use_graph:
-                self._enqueue_v5(h_r, r, par, Wd, Wq, M)
+                self._enqueue(h_r, resid, parity, Wd, Wq, M)
                 return self.out
+            key = (parity, M)
             if self.graph_bind:
-                hs, rs = h_r, r
-                key = (par, M, h_r.data_ptr(), r.data_ptr() if r is not None else 0)
+                key += (h_r.data_ptr(), resid.data_ptr() if resid is not None else 0)
             else:
                 self.h_static[:M].copy_(h_r)
-                if r is not None:
-                    self.resid_static[:M].copy_(r)
-                hs = self.h_static[:M]
-                rs = self.resid_static[:M] if r is not None else None
-                key = (par, M)
-            if not self._warm:               # un-captured first forward (the device epoch advances with the host epoch)
-                self._warm = True
-                self._enqueue_v5(hs, rs, par, Wd, Wq, M)
-                return self.out
-            g = self._graphs.get(key)
-            if g is None:
-                torch.cuda.synchronize(self.dev)
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self._enqueue_v5(hs, rs, par, Wd, Wq, M)
-                self._graphs[key] = g
-            g.replay()
+                h_r = self.h_static[:M]
+                if resid is not None:
+                    self.resid_static[:M].copy_(resid)
+                    resid = self.resid_static[:M]
+            self._graphs.run(key, lambda: self._enqueue(h_r, resid, parity, Wd, Wq, M))
             return self.out
 
     def x(self):
         """New residual (M, n1) of the most recent forward; valid until two forwards later (x is double-buffered)."""
-        if not self.protocol:
-            return self._floor_y[:self._last_M]
-        return self.xbufs[self._last_par][:self._last_M]
+        parity, M = self._last
+        return self._floor_y[:M] if not self.protocol else self.xbufs[parity][:M]
 
     def check(self):
         """Synchronise this rank's device and raise if a device-side wait gave up."""
         torch.cuda.synchronize(self.dev)
-        check_status(self.status, f"boundary rank {self.rank}")
+        check_status(self.buf.status, f"boundary rank {self.rank}")
 
     def trace_summary(self):
         """CTAPP_TRACE stamps of the most recent eager forward, in us relative to the first producer CTA's entry."""
         torch.cuda.synchronize(self.dev)
-        td, tq = self.trace_down.view(-1, 8).cpu(), self.trace_qkv.view(-1, 8).cpu()
-        td, tq = td[td[:, 0] > 0], tq[tq[:, 0] > 0]
-        if td.shape[0] == 0:
+        prod, cons = (t.view(-1, 8).cpu() for t in (self.trace_down, self.trace_qkv))
+        prod, cons = prod[prod[:, 0] > 0], cons[cons[:, 0] > 0]
+        if prod.shape[0] == 0:
             return {}
-        t0 = int(td[:, 0].min())
-        us = lambda v: (int(v) - t0) / 1e3  # noqa: E731
-        d = {"prod_ctas": int(td.shape[0]), "prod_entry_max": us(td[:, 0].max()), "prod_first_tile_max": us(td[:, 1].max()),
-             "prod_end_min": us(td[:, 7].min()), "prod_end_max": us(td[:, 7].max()), "cons_ctas": int(tq.shape[0])}
-        P = self._last_M // 128
-        tr = self.trace_red.cpu()[[m for m in range(P) if m % self.world == self.rank]]
-        if tr.numel() and int(tr.min()) > 0:
-            d["red_first_panel"], d["red_last_panel"] = us(tr.min()), us(tr.max())
-        if tq.shape[0]:
-            d["cons_entry_min"], d["cons_first_tile_min"] = us(tq[:, 0].min()), us(tq[:, 1].min())
-            d["cons_end_max"] = us(tq[:, 7].max())
-        return d
+        origin = int(prod[:, 0].min())
+        rel_us = lambda v: (int(v) - origin) / 1e3  # noqa: E731
+        out = {"prod_ctas": int(prod.shape[0]), "prod_entry_max": rel_us(prod[:, 0].max()), "prod_first_tile_max": rel_us(prod[:, 1].max()),
+               "prod_end_min": rel_us(prod[:, 7].min()), "prod_end_max": rel_us(prod[:, 7].max()), "cons_ctas": int(cons.shape[0])}
+        owned = torch.arange(self.rank, self._last[1] // 128, self.world)
+        pub = self.trace_red.cpu()[owned]
+        if pub.numel() and int(pub.min()) > 0:
+            out["red_first_panel"], out["red_last_panel"] = rel_us(pub.min()), rel_us(pub.max())
+        if cons.shape[0]:
+            out.update(cons_entry_min=rel_us(cons[:, 0].min()), cons_first_tile_min=rel_us(cons[:, 1].min()), cons_end_max=rel_us(cons[:, 7].max()))
+        return out
 
 
 def forward_lockstep(bds, h_rs, resids, Wds, Wqs):
@@ -348,25 +463,23 @@ def forward_lockstep(bds, h_rs, resids, Wds, Wqs):
     reducers, then all consumers.  When several ranks share a GPU (one device playing all ranks) no kernel is ever
     launched before the kernels it waits for, so nothing waits on the device; with one GPU per rank the phases of different
     ranks still overlap across GPUs.  Returns the list of per-rank outputs."""
-    outs = []
-    for bd, h in zip(bds, h_rs):
-        M = h.shape[0]
+    Ms = [h.shape[0] for h in h_rs]
+    for bd, M in zip(bds, Ms):
         bd.epoch += 1
-        bd._last_par, bd._last_M = bd.epoch & 1, M
+        bd._last = (bd.epoch & 1, M)
         bd.out = bd._out_full[:M]
         with torch.cuda.device(bd.dev):
-            bd.ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, M, bd.role_ctr)
-    for bd, h, Wd in zip(bds, h_rs, Wds):
+            bd._step(M)
+    for bd, h, Wd, M in zip(bds, h_rs, Wds, Ms):
         with torch.cuda.device(bd.dev):
-            bd._down_v5(h, Wd, h.shape[0])
-    for bd, h, r in zip(bds, h_rs, resids):
+            bd.launch_producer(h, Wd, M)
+    for bd, r, M in zip(bds, resids, Ms):
         with torch.cuda.device(bd.dev):
-            bd._reduce_v5(h.shape[0], r if bd.use_resid else None, bd._last_par)
-    for bd, h, Wq in zip(bds, h_rs, Wqs):
+            bd.launch_reducer(M, r if bd.use_resid else None, bd._last[0])
+    for bd, Wq, r, M in zip(bds, Wqs, resids, Ms):
         with torch.cuda.device(bd.dev):
-            bd._qkv_v5(Wq, h.shape[0], bd._last_par)
-        outs.append(bd.out)
-    return outs
+            bd.launch_consumer(Wq, M, bd._last[0], r if bd.use_resid else None)
+    return [bd.out for bd in bds]
 
 
 def _group_barrier(group):
@@ -496,45 +609,6 @@ class AsyncTpBoundary(_Base):
         self._x = ys                                             # own rows only
         dist.all_gather_into_tensor(self.full, rmsnorm_gamma(ys, self.gamma))
         return torch.mm(self.full, self.Wq.t())
-
-
-class FlashInferBoundary(_Base):
-    """cuBLAS GEMM + FlashInfer's fused all-reduce + residual + RMSNorm kernel (the serving stacks' production path) + cuBLAS
-    GEMM (reference ctapp/tp4.py:586-618).  The reduction is not overlapped with the GEMM.  FlashInfer builds its kernels on
-    first use."""
-
-    def __init__(self, *a, use_oneshot=None):
-        super().__init__(*a)
-        from flashinfer.comm import trtllm_create_ipc_workspace_for_all_reduce_fusion as create
-        n1 = self.Wd.shape[0]
-        self.use_oneshot = use_oneshot
-        self.ipc, self.ws = create(self.rank, self.world, self.M, n1, group=dist.group.WORLD)[:2]
-        self.y = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.resid_out = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.norm_out = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.zeros = None
-        self.gamma_c = self.gamma.contiguous()
-
-    def forward(self, h_r, resid=None):
-        from flashinfer.comm import AllReduceFusionPattern, trtllm_allreduce_fusion
-        if resid is None:
-            if self.zeros is None:
-                self.zeros = torch.zeros_like(self.y)
-            resid = self.zeros
-        torch.mm(h_r, self.Wd.t(), out=self.y)
-        trtllm_allreduce_fusion(allreduce_in=self.y, world_size=self.world, world_rank=self.rank, token_num=self.M, hidden_dim=self.y.shape[1],
-                                workspace_ptrs=self.ws, launch_with_pdl=False, trigger_completion_at_end=True, fp32_acc=True,
-                                pattern_code=AllReduceFusionPattern.kARResidualRMSNorm, use_oneshot=self.use_oneshot, allreduce_out=None,
-                                residual_in=resid, residual_out=self.resid_out, norm_out=self.norm_out, quant_out=None, scale_out=None,
-                                rms_gamma=self.gamma_c, rms_eps=EPS, scale_factor=None, layout_code=None)
-        self._x = self.resid_out
-        return torch.mm(self.norm_out, self.Wq.t())
-
-    def destroy(self):
-        from flashinfer.comm import trtllm_destroy_ipc_workspace_for_all_reduce_fusion as destroy
-        torch.cuda.synchronize(self.dev)
-        dist.barrier()
-        destroy(self.ipc)
 
 
 # --------------------------------------------------------------------------- references

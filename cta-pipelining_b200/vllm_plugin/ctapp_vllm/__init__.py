@@ -20,15 +20,21 @@ def knobs(env=None):
         raise ValueError(f"CTAPP_BOUNDARY={mode!r}: expected both | down | oproj")
     if proto not in ("v3", "v5"):
         raise ValueError(f"CTAPP_PROTO={proto!r}: expected v3 | v5")
-    if fusion not in ("none", "pdl"):
-        raise ValueError(f"CTAPP_FUSION={fusion!r}: this build has none | pdl")
+    if fusion not in ("none", "pdl", "pdl1"):
+        raise ValueError(f"CTAPP_FUSION={fusion!r}: this build has none | pdl | pdl1 (role: use CTAPP_STEAL=1)")
     tile = int(e.get("CTAPP_QKV_TILE", "256"))
     if tile not in (128, 256):
         raise ValueError(f"CTAPP_QKV_TILE={tile}: expected 128 | 256")
     return {"enabled": e.get("CTAPP_VLLM", "0") == "1", "boundary": mode, "proto": proto, "fusion": fusion, "qkv_tile": tile,
             "max_M": int(e.get("CTAPP_MAX_M", "8192")), "min_M": int(e.get("CTAPP_MIN_M", "512")),
             "R": int(e["CTAPP_R"]) if e.get("CTAPP_R") else None, "check": e.get("CTAPP_CHECK", "0") == "1",
-            "log_M": e.get("CTAPP_LOG_M", "0") == "1", "steal": e.get("CTAPP_STEAL")}
+            "log_M": e.get("CTAPP_LOG_M", "0") == "1", "cksum": e.get("CTAPP_CKSUM", "0") == "1",
+            # CTAPP_STEAL unset: boundary A steals, B does not (the reference's default); set: both boundaries follow it
+            "steal_a": e.get("CTAPP_STEAL", "1") == "1", "steal_b": e.get("CTAPP_STEAL", "0") == "1",
+            # consumer tile orders (raster 2 = n fastest, 3 = groups of `swizzle` tile rows, else m fastest); the defaults are
+            # the orders measured best with this library's kernels, not the reference's CUTLASS raster numbers
+            "a_raster": int(e.get("CTAPP_A_RASTER", "3")), "a_swizzle": int(e.get("CTAPP_A_SWIZZLE", "4")),
+            "b_raster": int(e.get("CTAPP_B_RASTER", "2")), "b_swizzle": int(e.get("CTAPP_B_SWIZZLE", "1"))}
 
 
 def register():

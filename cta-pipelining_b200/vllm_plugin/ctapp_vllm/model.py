@@ -85,9 +85,13 @@ class CtappLlamaModel(LlamaModel):
         common = dict(R=k["R"], min_M=k["min_M"], protocol=k["proto"], max_M=k["max_M"], fusion=k["fusion"], n1=hidden,
                       eps=self.config.rms_norm_eps)
         self._pool_b = CtappBoundaryPool(l0.mlp.down_proj.weight.shape[1], l0.self_attn.qkv_proj.weight.shape[0], rank, t, group, device,
-                                         qkv_raster=2, qkv_swizzle=1, qkv_tile=k["qkv_tile"], **common)
+                                         qkv_raster=k["b_raster"], qkv_swizzle=k["b_swizzle"], qkv_tile=k["qkv_tile"], steal=k["steal_b"], **common)
         self._pool_a = CtappBoundaryPool(l0.self_attn.o_proj.weight.shape[1], l0.mlp.gate_up_proj.weight.shape[0], rank, t, group, device,
-                                         qkv_raster=3, qkv_swizzle=4, qkv_tile=256, down_tail=hidden // 256, **common)
+                                         qkv_raster=k["a_raster"], qkv_swizzle=k["a_swizzle"], qkv_tile=256, down_tail=hidden // 256,
+                                         steal=k["steal_a"], **common)
+        if k["cksum"] and rank == 0:
+            w = l0.mlp.down_proj.weight.float()
+            logger.warning("CTAPP_CKSUM layers[0].down_proj.weight rank0 shape=%s sum=%.6e abssum=%.6e", tuple(w.shape), w.sum().item(), w.abs().sum().item())
         logger.warning("ctapp_vllm rank %d: set-up done (%s)", rank, {kk: v for kk, v in k.items() if kk != "enabled"})
 
     def _boundaries(self, M):

@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 2 */
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 3 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);
@@ -99,6 +99,18 @@ typedef struct ctapp_chain_args {     /* ctapp.cuh:7-19 */
                                          panels of this GEMM): windows of any sizes, for a producer that finishes its
                                          row panels in groups of varying size; overrides src_group.  NULL = off. */
   int n_windows;
+  /* k-chunk dependencies (no counterpart in the reference, whose consumer tile waits for its complete row panel,
+   * ctapp.cuh:32-48, 51-69): value flags, one per tile of the PRODUCING GEMM, in the consuming GPU's memory.
+   *   chunk_dst   producer side: peer address of the next GPU's flags; finished tile (m, n) raises chunk_dst[m * tiles_n + n] =
+   *               chunk_value after its rows have landed (may be combined with dep_offsets; NULL = off)
+   *   chunk_src   consumer side: this GPU's flags [row tiles][chunk_cols]; before loading the k-blocks
+   *               [c * chunk_kblocks, (c + 1) * chunk_kblocks) of a tile of row tile m the loader waits (bounded) for
+   *               chunk_src[m * chunk_cols + c] >= chunk_value, so a tile's main loop streams behind the producer.  The source
+   *               queue is then pre-filled with this GEMM's own tile order (cap ids, tail = cap).  Both GEMMs must use tiles of the
+   *               same height.  Values only grow from run to run, so the flags are never reset. */
+  int* chunk_dst;
+  const int* chunk_src;
+  int chunk_kblocks, chunk_cols, chunk_value;
 } ctapp_chain_args;
 
 /* One stage of the chain: Y = X * W^T with tile ids popped from args->src and completion published into args->dst.
@@ -126,10 +138,14 @@ typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0
   unsigned long long* trace;
   int* status;
   int cta_pair;                            /* 1 = two CTAs per 256-row tile (cta_group::2), 0 = one CTA per 128-row tile */
+  int* tile_log;                           /* NULL, or [0] = 0 on entry and room for 1 + #tiles ints: the kernel appends one packed
+                                              (m << 16 | n) per tile in the order its schedulers take them (m = tile row of the
+                                              schedule: 256 rows with cta_pair); with one CTA (pair) that is the tile order itself */
 } ctapp_tp_down_args;
 int ctapp_tp_down(const ctapp_tp_down_args* args, int device, void* stream);
 
-typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 and 5 */
+struct ctapp_tp_reduce_args;
+typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0, 5 and 8 */
   const void* X; const void* W; void* Y;   /* X (M,K) local, written by the owner reducers; W (N,K) gamma-folded; Y (M,N) */
   int M, N, K;
   int raster, swizzle, mode;               /* raster 2: n fastest; 3: groups of `swizzle` tile rows, n-major inside; else m fastest */
@@ -146,6 +162,12 @@ typedef struct ctapp_tp_qkv_args {    /* gemm_tp4.cu:319-359 (tp4_qkv); modes 0 
                                               factors rounded to bf16 first; needs cta_pair.  The reference runs the
                                               activation as a separate kernel (vllm_plugin/ctapp_vllm/model.py:183) and
                                               lists this fusion as future work (PLAN.md:597).  0 = off. */
+  const struct ctapp_tp_reduce_args* red;  /* mode 8 (csrc/ctapp_tp4.cuh:913-925, the work-stealing form of tp4_role_preamble):
+                                              every warp of every CTA first claims owner-reducer units from red->unit_ctr until
+                                              none are left, then the CTA runs its GEMM tiles as in mode 5.  CTAs that become
+                                              resident as the producer's retire thus drain what the dedicated reducer CTAs
+                                              (ctapp_tp_reduce with the same unit_ctr) have not reached.  red->blocks / threads
+                                              are ignored.  NULL in the other modes. */
 } ctapp_tp_qkv_args;
 int ctapp_tp_qkv(const ctapp_tp_qkv_args* args, int device, void* stream);
 
@@ -161,8 +183,16 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   int* peer_panel_flag[CTAPP_MAX_WORLD];    /* panel_flag of every rank, [M/128] */
   float* rowss_local;                       /* [M] accumulators, zeroed by ctapp_tp_step */
   int* panel_done;                          /* [M/128] arrival counters, zeroed by ctapp_tp_step */
-  int panels_per_owner, tail_cols;
-  int* unit_ctr;                            /* NULL = static unit assignment */
+  int panels_per_owner, tail_cols;          /* panels_per_owner: the ppo the flags and inbox were allocated with; must be
+                                               >= ceil(M / 128 / world) (checked) and not larger than the allocation (the caller's) */
+  int order, swz;                           /* unit order when tail_cols == 0 (csrc/ctapp_tp4.cuh:551-565): order 0 | 1 = m fastest,
+                                               in groups of swz n-tiles when swz > 1; 2 = panel by panel */
+  int* unit_ctr;                            /* NULL = static unit assignment; else units are claimed from this counter (zeroed
+                                               per step, e.g. role_ctr + 1 of ctapp_tp_step), which ctapp_tp_qkv mode 8 shares */
+  int* unit_log;                            /* NULL, or [0] = 0 on entry and room for 1 + #units ints: one packed
+                                               (j << 16 | n << 2 | q) per unit in the order the warps take them */
+  int pdl_trigger;                          /* 1: raise the programmatic-launch trigger at entry, so that a producer GEMM
+                                               launched behind this kernel with pdl = 1 starts beside it (ctapp/tp4.py:316-320) */
   unsigned long long* trace;
   int* status;
   /* NVLS variant (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.st / multimem.red pushes): multicast addresses of the x
@@ -170,9 +200,6 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   void* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
-  /* 1 = TMA-fed kernel (loader warp stages 32 x 256 patches of every source in shared memory, 8 adder warps, a publisher
-   * warp; `threads` is ignored, `blocks` CTAs of 320 threads); 0 = warp-per-unit kernel with register loads */
-  int tma;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 
@@ -183,15 +210,29 @@ int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
  * working memory -- the per-row fp32 accumulators and the per-panel arrival counters that ctapp_tp_reduce takes as
  * rowss_local / panel_done -- in a fixed array inside the library (66 048 bytes, resident on every GPU that loads the
  * library until the process exits).  The caller passes inputs and outputs exactly as for ctapp_tp_reduce;
- * args->rowss_local, args->panel_done and args->unit_ctr are ignored, and no ctapp_tp_step is needed for them: the
- * call zeroes the part of the array it uses (stream-ordered, before the kernel).
+ * args->rowss_local and args->panel_done are ignored, and no ctapp_tp_step is needed for them: the call zeroes the part of
+ * the array it uses (stream-ordered, before the kernel).  What this variant does not offer is refused with an argument
+ * error rather than ignored: the NVLS pushes (x_mc, rowss_mc, panel_flag_mc must be NULL: it pushes with unicast stores),
+ * dynamic unit claims and the unit log (unit_ctr, unit_log must be NULL) and pdl_trigger (must be 0).
  *   Limit: M <= 16384 rows; larger M is refused with an error naming the limit.
- *   The first call on a device looks up the array's device address (one cudaGetSymbolAddress, no allocation); make
- *   that first call outside any stream capture.
+ *   The first call on a device looks up the array's device address (one cudaGetSymbolAddress, no allocation) unless
+ *   ctapp_preload has run on that device, which does the same look-up; make whichever comes first outside any stream capture.
  *   All calls on a GPU share the one array: two calls whose kernels overlap on the GPU (different streams) race on
  *   it.  Issue them on one stream, or order them with events.
  * The call performs no cudaMalloc / cudaFree and uses no allocating library routine. */
 int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* args, int device, void* stream);
+
+/* Read-back of the integer maps the kernels schedule by, computed by the same device functions (no counterpart in the
+ * reference, where tp4_remap_tile / red5_map, csrc/ctapp_tp4.cuh:897-906, 551-565, exist only inside the kernels):
+ *   tile order  out_mn[2 L], out_mn[2 L + 1] = (m, n) of schedule position L; order 0 = groups of group_rows tile rows, n-major
+ *               inside a group; 1 = m fastest over the first tiles_n - tail_cols n-tiles, then tile row by tile row over the
+ *               last tail_cols; 2 = n fastest
+ *   unit order  out_jnq[3 u ..] = (owned panel j, n-tile, quarter) of the owner reducer's unit u
+ *   queue slots out_slots[i] = source-queue slot read by the i-th pop of a consuming chain stage (src_group / src_windows) */
+int ctapp_debug_tile_order(int order, int tiles_m, int tiles_n, int group_rows, int tail_cols, int* out_mn, int device, void* stream);
+int ctapp_debug_unit_order(int owned_panels, int tiles_n, int tail_cols, int order, int swz, int* out_jnq, int device, void* stream);
+int ctapp_debug_queue_slots(int num_tiles, int tiles_n, int src_group, const int* src_windows, int n_windows, int* out_slots,
+                            int device, void* stream);
 
 /* epoch_dev[0] += 1; zero rowss_local[0:M], panel_done[0:M/128] and role_ctr[0:2].  gemm_tp4.cu:362-372 (tp4_step). */
 int ctapp_tp_step(int* epoch_dev, float* rowss_local, int* panel_done, int M, int* role_ctr, int device, void* stream);

@@ -55,15 +55,44 @@ def remap_tile(L, TM, TN, C):
     return L2 // C, TN - C + L2 % C
 
 
-def unit_map(u, Pr, tiles_n, tail):
+def unit_map(u, Pr, tiles_n, tail, order=1, swz=1):
     """Reducer unit u -> (owned panel j, n-tile, quarter q), following the producer order restricted to
-    this rank's panels   (csrc/ctapp_tp4.cuh:551-565, tail and order-1/swizzle-1 branches)."""
+    this rank's panels   (csrc/ctapp_tp4.cuh:551-565): the tail order when tail > 0; otherwise order 1 = m fastest
+    (n-major; with swz > 1 in groups of swz n-tiles: for each group, for each owned panel, the group's n-tiles),
+    order 2 = panel by panel."""
     q, t = u % QUARTERS, u // QUARTERS
-    head = Pr * (tiles_n - tail)
-    if t < head:
+    if tail > 0:
+        head = Pr * (tiles_n - tail)
+        if t < head:
+            return t % Pr, t // Pr, q
+        t2 = t - head
+        return t2 // tail, tiles_n - tail + t2 % tail, q
+    if order == 2:
+        return t // tiles_n, t % tiles_n, q
+    if swz <= 1:
         return t % Pr, t // Pr, q
-    t2 = t - head
-    return t2 // tail, tiles_n - tail + t2 % tail, q
+    g = t // swz
+    return g % Pr, (g // Pr) * swz + t % swz, q
+
+
+def tile_order(order, TM, TN, group_rows=1, tail=0):
+    """(m, n) of every schedule position of a GEMM with TM x TN tiles, for the three static orders of the kernels: 0 = groups of
+    ``group_rows`` tile rows, n-major inside a group (the last group may be short); 1 = ``remap_tile`` with ``tail`` columns;
+    2 = n fastest.  Order 1 restates csrc/ctapp_tp4.cuh:897-906; order 0 is the chain's grouped producer order
+    (ctapp/pipeline.py:48-51) as a position -> tile function; order 2 is row-major."""
+    out = []
+    for L in range(TM * TN):
+        if order == 2:
+            out.append((L // TN, L % TN))
+        elif order == 1:
+            out.append(remap_tile(L, TM, TN, tail))
+        else:
+            g = max(group_rows, 1)
+            grp, r = divmod(L, g * TN)
+            m0 = grp * g
+            rows = min(g, TM - m0)
+            out.append((m0 + r % rows, r // rows))
+    return out
 
 
 def tile_flag_index(src, j, n, ppo, tiles_n=N1 // UNIT_COLS):

@@ -123,6 +123,24 @@ def simulate_link(M, N1, N2, BM1, BN1, BM2, BN2, rowpanel=True, group_rows=0, or
     return q.entries.astype(np.int32), q.tail, q.sb.astype(np.int32)
 
 
+def simulate_kchunk_link(order1, tn1, order2, tn2, chunks, run_id=1):
+    """Sequential model of one link with k-chunk dependencies (value flags per producer tile instead of a scoreboard and a
+    queue): the producer finishes its tiles in ``order1`` (ids m * tn1 + n) and raises flag[m, n] = run_id; consumer tile
+    m * tn2 + n2 may load k-chunk c once flag[m, c] is up.  Returns (flags after the run, for every consumer tile in
+    ``order2`` the number of producer tiles that must have finished before it can complete).  The second array is the
+    readiness order of a serialised device run; a consumer that walks ``order2`` never waits for a tile that a producer
+    walking ``order1`` has not been able to start (there is no back edge), so the pair cannot deadlock."""
+    order1, order2 = np.asarray(order1).astype(np.int64), np.asarray(order2).astype(np.int64)
+    tm = order1.size // tn1
+    done_at = np.empty(order1.size, dtype=np.int64)
+    done_at[order1] = np.arange(1, order1.size + 1)
+    done_at = done_at.reshape(tm, tn1)
+    assert chunks <= tn1
+    need = np.array([done_at[t // tn2, :chunks].max() for t in order2], dtype=np.int64)
+    flags = np.full((tm, tn1), run_id, dtype=np.int32)
+    return flags, need
+
+
 def check_link_invariants(entries, tail, scoreboard, n_consumer_tiles, tiles_n2, rowpanel):
     """Order-independent invariants every (concurrent) run must satisfy.  Returns a list of violations."""
     bad = []

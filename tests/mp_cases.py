@@ -75,7 +75,7 @@ def nvls_probes(rank, world, dev, gn):
     return fails
 
 
-def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N2_, red_variant=3):
+def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N2_, steal=False):
     """The boundary with one process per GPU against the CPU oracle; also x identical on every rank and flags == epoch."""
     import sys, os
     from ctapp import tp4
@@ -87,7 +87,7 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     fails = []
     Kr, N2r = K // world, N2_ // world
     max_M = max(Ms)
-    bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, red_variant=red_variant)
+    bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, steal=steal)
     if protocol == "v3" and not bd.nvls:
         return ["SKIP: no multicast address on this system"]
     for it, M in enumerate(Ms):

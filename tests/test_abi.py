@@ -31,7 +31,7 @@ def test_argument_errors_without_gpu():
     """Calls that fail in argument checking never touch CUDA, so they can run here."""
     from ctapp import ext
     lib = ext.lib()
-    assert lib.ctapp_abi_version() == 2
+    assert lib.ctapp_abi_version() == ext.ABI_VERSION == 3
     buf = ctypes.create_string_buffer(256)
     assert lib.ctapp_config_info(3, buf, 256) == 0 and b"tile 128x256x64" in buf.value
     assert lib.ctapp_config_info(5, buf, 256) == 0 and b"tile 128x128x64" in buf.value
@@ -44,6 +44,39 @@ def test_argument_errors_without_gpu():
     assert lib.ctapp_gate_set(1) < 0 and b"gate_alloc" in lib.ctapp_last_error()
 
 
+def _reduce_args(**over):
+    """A reducer argument block with fake (never dereferenced) addresses: argument checking happens before any CUDA call."""
+    from ctapp import ext
+    fake = 0x1000
+    kw = dict(M=1024, rank=0, world=2, epoch=1, epoch_dev=None, blocks=4, threads=1024, tile_flags=fake, inbox_ptrs=[fake, fake], resid=None,
+              peer_x=[fake, fake], peer_rowss=[fake, fake], peer_panel_flag=[fake, fake], rowss_local=fake, panel_done=fake, panels_per_owner=4,
+              tail_cols=8, n1=8192, status=None)
+    kw.update(over)
+    return ext.Tp4Module._reduce_args(**kw)
+
+
+def test_reducer_argument_checks_without_gpu():
+    """panels_per_owner is validated (a value below ceil(M / 128 / world) would make the sources' tile flags alias each other),
+    and the allocation-free variant refuses what it does not do instead of ignoring it."""
+    from ctapp import ext
+    lib = ext.lib()
+    a = _reduce_args(panels_per_owner=3)
+    assert lib.ctapp_tp_reduce(ctypes.byref(a), 0, None) == -1 and b"panels_per_owner" in lib.ctapp_last_error()
+    assert lib.ctapp_tp_reduce_noalloc(ctypes.byref(a), 0, None) == -1 and b"panels_per_owner" in lib.ctapp_last_error()
+    with pytest.raises(RuntimeError):
+        _reduce_args(panels_per_owner=0)                       # the binding insists on the argument
+    for over, word in ((dict(x_mc_ptr=0x2000, rowss_mc_ptr=0x2000, panel_flag_mc_ptr=0x2000), b"unicast"), (dict(unit_ctr=0x2000), b"unit_ctr"),
+                       (dict(unit_log=0x2000), b"unit_ctr"), (dict(pdl_trigger=1), b"pdl_trigger"), (dict(M=32768, panels_per_owner=128), b"16384")):
+        a = _reduce_args(**over)
+        assert lib.ctapp_tp_reduce_noalloc(ctypes.byref(a), 0, None) == -1, over
+        assert word in lib.ctapp_last_error(), (over, lib.ctapp_last_error())
+    a = _reduce_args(order=3)
+    assert lib.ctapp_tp_reduce(ctypes.byref(a), 0, None) == -1
+    q = ext.TpQkvArgs()
+    q.mode = 8
+    assert lib.ctapp_tp_qkv(ctypes.byref(q), 0, None) == -1 and b"mode 8" in lib.ctapp_last_error()
+
+
 def test_python_module_surface():
     """The two module objects carry the function names of the reference's extension modules."""
     from ctapp import ext
@@ -51,7 +84,7 @@ def test_python_module_surface():
     for name in ("gemm_tma", "ctapp_gemm", "coop_gemm", "coop_info", "config_info", "occupancy", "enable_peer_access",
                  "p2p_store_bw_kernel", "gate_alloc", "gate_set", "gate_wait", "peer_copy", "stamp_now", "timer_reads", "pingpong"):
         assert callable(getattr(m1, name)), name
-    for name in ("tp4_down", "tp4_qkv", "tp4_reduce", "tp4_step", "tp4_info", "tp4_set_debug"):
+    for name in ("tp4_down", "tp4_qkv", "tp4_reduce", "tp4_reduce_noalloc", "tp4_step", "tp4_info", "tp4_set_debug"):
         assert callable(getattr(m2, name)), name
     assert "tile 128x256x64" in m1.config_info(3)
     with pytest.raises(RuntimeError):

@@ -74,19 +74,91 @@ def _forward_and_check(bds, M, K, n1, N2_, seed, use_resid=True):
         assert int(bd.epoch_dev.item()) == bd.epoch
 
 
-@pytest.mark.parametrize("cta_pair,red_variant", [(True, 3), (True, 1), (False, 3), (False, 1)])
+@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (True, dict(steal=True)), (False, dict(down_raster=2)), (False, dict(steal=True, down_tail=0))])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
-def test_boundary_one_gpu_plays_all_ranks(world, cta_pair, red_variant):
+def test_boundary_one_gpu_plays_all_ranks(world, cta_pair, kw):
+    """``steal`` here: the dedicated reducers claim their units from the shared counter and the mode-8 consumers, launched after
+    them, find it exhausted; ``down_raster=2``: producer and reducer walk panel by panel."""
     K, n1, N2_ = 1024 * world if world < 8 else 2048, 512, 256 * world
-    bds = _setup(world, [0] * world, 1024, K, n1, N2_, cta_pair=cta_pair, red_variant=red_variant)
+    bds = _setup(world, [0] * world, 1024, K, n1, N2_, cta_pair=cta_pair, **kw)
     for seed, M in enumerate((1024, 256, 640, 128), start=3):   # variable M on one instance, fresh weights per call
         _forward_and_check(bds, M, K, n1, N2_, seed)
 
 
 def test_boundary_no_residual_and_tile128():
-    bds = _setup(2, [0, 0], 512, 512, 768, 512, resid=False, qkv_tile=128, down_tail=0, red_variant=3)
+    bds = _setup(2, [0, 0], 512, 512, 768, 512, resid=False, qkv_tile=128, down_tail=0)
     _forward_and_check(bds, 512, 512, 768, 512, 11, use_resid=False)
     _forward_and_check(bds, 384, 512, 768, 512, 12, use_resid=False)
+
+
+@pytest.mark.parametrize("cta_pair", [True, False])
+def test_consumer_ctas_do_the_whole_reduction(cta_pair):
+    """``steal`` with no dedicated reducer CTAs (R = 0): every unit is claimed and reduced by warps of the consumer GEMM's CTAs
+    before they start on their tiles (one rank; with more ranks on one GPU a consumer would wait for panels whose owners'
+    consumers have not been launched yet)."""
+    bds = _setup(1, [0], 1024, 1024, 1024, 768, cta_pair=cta_pair, steal=True, R=0)
+    for seed, M in enumerate((1024, 384, 1024), start=40):
+        _forward_and_check(bds, M, 1024, 1024, 768, seed)
+        assert int(bds[0].role_ctr[1].item()) >= (M // 128) * (1024 // 256) * 4      # every unit was claimed from the counter
+
+
+def test_boundary_headline_shape_vs_oracle():
+    """The benchmarked boundary shape -- M = 4096 tokens, down-projection K = 28672 (two ranks of 14336), hidden 8192, QKV width
+    10240 -- with one GPU playing both ranks, against the CPU oracle (about 5 TFLOP on the host cores)."""
+    bds = _setup(2, [0, 0], 4096, 28672, 8192, 10240)
+    _forward_and_check(bds, 4096, 28672, 8192, 10240, 77)
+
+
+def test_thirty_forwards_alternating_shapes_and_inputs():
+    """Back-to-back stress (reference tests/test_tp4.py:216-263): 30 forwards on one instance without a host synchronisation
+    in between, alternating (M, inputs, weights); every output and x is cloned on the stream and checked afterwards."""
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundary
+    K, n1, N2_, max_M = 512, 1024, 512, 1024
+    bd = CtappBoundary(max_M, K, N2_, 0, 1, LocalGroup([0]), torch.device("cuda", 0), protocol="v5", n1=n1, fusion="serial")
+    cases = []
+    for i, M in enumerate((1024, 256, 768, 128)):
+        Wd, gamma, Wq = ob.make_weights(seed=80 + i, K=K, N2_=N2_, n1=n1)
+        h, resid = ob.make_inputs(M, seed=90 + i, K=K, n1=n1)
+        wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, 0, 1)
+        cases.append((h.cuda(), resid.cuda(), wd.cuda(), wqf.cuda(), ob.boundary_device_model(h, Wd, resid, gamma, Wq, 1)))
+    got = []
+    for it in range(30):
+        h, resid, wd, wqf, _ = cases[(it * 3 + it // 4) % 4]
+        out = bd.forward(h, resid, wd, wqf)
+        got.append((out.clone(), bd.x().clone()))
+    bd.check()
+    for it, (out, x) in enumerate(got):
+        x_model, out_model = cases[(it * 3 + it // 4) % 4][4]
+        assert _ulp_frac(x.cpu(), x_model) >= 0.99 and _ulp_frac(out.cpu(), out_model) >= 0.98, it
+    assert bd.epoch == 30 and int(bd.epoch_dev.item()) == 30
+
+
+def test_fifty_forwards_cycling_M_eager_and_graphs():
+    """Soak (reference tests/test_tp4.py:266-300): 50 forwards cycling the token count, eager and with one CUDA graph per
+    (parity, M); the last output of every M is checked and the device epoch must have followed the host's."""
+    from ctapp.symm import LocalGroup
+    from ctapp.tp4 import CtappBoundary
+    K, n1, N2_, max_M = 512, 512, 512, 1024
+    Wd, gamma, Wq = ob.make_weights(seed=7, K=K, N2_=N2_, n1=n1)
+    wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, 0, 1)
+    Ms = (1024, 512, 256, 768, 128)
+    data = {M: ob.make_inputs(M, seed=M, K=K, n1=n1) for M in Ms}
+    model = {M: ob.boundary_device_model(data[M][0], Wd, data[M][1], gamma, Wq, 1) for M in Ms}
+    for use_graph in (False, True):
+        bd = CtappBoundary(max_M, K, N2_, 0, 1, LocalGroup([0]), torch.device("cuda", 0), protocol="v5", n1=n1, fusion="serial", use_graph=use_graph)
+        bd.set_weights(wd.cuda(), wqf.cuda())
+        last = {}
+        for it in range(50):
+            M = Ms[it % len(Ms)] if it % 7 else Ms[(it // 7) % len(Ms)]
+            out = bd.forward(data[M][0].cuda(), data[M][1].cuda())
+            last[M] = (out.clone(), bd.x().clone())
+        bd.check()
+        assert int(bd.epoch_dev.item()) == bd.epoch == 50
+        if use_graph:
+            assert 2 <= len(bd._graphs.graphs) <= 2 * len(Ms)      # one graph per (parity, M) seen after the first, eager, forward
+        for M, (out, x) in last.items():
+            assert _ulp_frac(x.cpu(), model[M][0]) >= 0.99 and _ulp_frac(out.cpu(), model[M][1]) >= 0.98, (use_graph, M)
 
 
 def test_boundary_hidden_8192_one_rank_vs_oracle():
@@ -128,8 +200,8 @@ def test_reducer_missing_producer_times_out_cleanly():
         bds = _setup(1, [0], 256, 256, 512, 256)
         bd = bds[0]
         bd.epoch += 1
-        ext.tp4_step(bd.epoch_dev, bd.rowss_local, bd.panel_done, 256, bd.role_ctr)
-        bd._reduce_v5(256, None, 1)
+        bd._step(256)
+        bd.launch_reducer(256, None, 1)
         torch.cuda.synchronize()
         s = bd.status.cpu().tolist()
         assert s[0] == 3 and s[3] == 1, s
@@ -156,16 +228,16 @@ def test_add_rmsnorm_baseline_kernel():
 
 
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("cta_pair,red_variant", [(True, 3), (False, 1), (True, 1)])
-@pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl")])
-def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, red_variant):
+@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (False, {}), (True, dict(steal=True)), (True, dict(steal=True, R=0)), (False, dict(steal=True))])
+@pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl"), (2, "pdl1")])
+def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, kw):
     """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""
     from ctapp.symm import LocalGroup
     from ctapp.tp4 import CtappBoundary
     K, n1, N2_, max_M = 4096, 8192, 2560, 2048
     grp = LocalGroup(list(range(world)))
     Kr, N2r = K // world, N2_ // world
-    bds = [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", r), protocol="v5", max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, red_variant=red_variant) for r in range(world)]
+    bds = [CtappBoundary(max_M, Kr, N2r, r, world, grp, torch.device("cuda", r), protocol="v5", max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, **kw) for r in range(world)]
     Wd, gamma, Wq = ob.make_weights(seed=1, K=K, N2_=N2_, n1=n1)
     sh = [ob.shard_weights(Wd, Wq, gamma, r, world) for r in range(world)]
     wds = [sh[r][0].to(bds[r].dev) for r in range(world)]; wqs = [sh[r][2].to(bds[r].dev) for r in range(world)]

@@ -54,10 +54,11 @@ def test_chain_one_gpu_small(case):
     assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
 
 
-@pytest.mark.parametrize("cfg", [3, 10])
-def test_chain_one_gpu_headline_config_vs_oracle(cfg):
-    """M=1024, N=K=8192 (the CPU-checkable configuration), 128x256 tiles and CTA-pair 256x256 tiles, grouped producer order."""
-    pl, X, W1, W2 = _run_case(1024, 8192, 8192, 8192, cfg, cfg, 0, 0, runs=2, fence=1, group_rows=8 if cfg == 3 else 4)
+@pytest.mark.parametrize("cfg,group_rows", [(3, 8), (10, 4), (11, 4), (11, 8), (11, "head")])
+def test_chain_one_gpu_headline_config_vs_oracle(cfg, group_rows):
+    """M=1024, N=K=8192 (the CPU-checkable configuration) on 128x256 tiles, CTA-pair 256x256 tiles and the benchmark's CTA-pair
+    256x512 tiles, in the producer orders the benchmark uses (groups of 8 tile rows; head-ramped groups)."""
+    pl, X, W1, W2 = _run_case(1024, 8192, 8192, 8192, cfg, cfg, 0, 0, runs=2, fence=1, group_rows=group_rows)
     ys = oc.chain_reference(X, [W1, W2], keep=True)
     for got, ref, name in ((pl.Y1, ys[0], "Y1"), (pl.Y2, ys[1], "Y2")):
         mx, mean = oc.error_stats(got.cpu(), ref)
@@ -82,6 +83,82 @@ def test_chain_serialised_order_is_bit_exact(rowpanel, cfg):
     assert np.array_equal(ch.sb[0].cpu().numpy(), sb)
     mx, mean = oc.error_stats(ch.Y[1].cpu(), oc.chain_reference(X, Ws))
     assert mx <= 2e-2 and mean <= 1e-3
+
+
+def _kchunk_case(M, K, N1, N2, cfg1, cfg2, devA, devB, group_rows, runs=3):
+    """A two-stage chain with k-chunk dependencies: both outputs bit-identical to the same kernels run one after the other, every
+    flag == the run's number afterwards (the oracle's model of the link), every tile taken exactly once."""
+    from ctapp.pipeline import Pipeline
+    pl = Pipeline(M, K, N1, N2, cfg1, cfg2, devA=devA, devB=devB, group_rows=group_rows, scoreboard="kchunk")
+    ch = pl.chain
+    X, (W1, W2) = oc.make_chain_inputs(M, K, [N1, N2], seed=0)
+    Xa, W1a, W2b = X.to(pl.a), W1.to(pl.a), W2.to(pl.b)
+    Y1s = torch.empty(M, N1, dtype=torch.bfloat16, device=pl.a)
+    pl.ext.gemm_tma(Xa, W1a, Y1s, cfg1)
+    Y1s_b = Y1s.to(pl.b)
+    Y2s = torch.empty(M, N2, dtype=torch.bfloat16, device=pl.b)
+    with torch.cuda.device(pl.b):
+        pl.ext.gemm_tma(Y1s_b, W2b, Y2s, cfg2)
+    torch.cuda.synchronize(pl.a); torch.cuda.synchronize(pl.b)
+    BM, BN1 = pl.tile(cfg1)
+    for r in range(1, runs + 1):
+        with torch.cuda.device(pl.b):
+            pl.Y1.fill_(float("nan")); pl.Y2.fill_(float("nan"))
+        torch.cuda.synchronize(pl.b)
+        pl.run(Xa, W1a, W2b)
+        pl.check()
+        assert torch.equal(pl.Y1, Y1s_b) and torch.equal(pl.Y2, Y2s), f"run {r}: the streamed chain differs from the sequential one"
+        flags, need = oc.simulate_kchunk_link(ch.entries[0].cpu().numpy(), ch.tn[0], ch.entries[1].cpu().numpy(), ch.tn[1], -(-N1 // BN1), run_id=r)
+        assert np.array_equal(ch.chunk[1].cpu().numpy(), flags)
+        assert need.max() <= ch.ntiles[0]
+        assert int(ch.head[0].item()) >= ch.ntiles[0] and int(ch.head[1].item()) >= ch.ntiles[1]
+    return pl, X, W1, W2
+
+
+@pytest.mark.parametrize("case", [(512, 512, 1024, 768, 10, 10, 2), (768, 256, 1536, 1024, 10, 11, 2), (1024, 512, 1024, 1024, 11, 11, 4),
+                                  (640, 512, 768, 512, 3, 3, 2), (1024, 256, 1024, 512, 11, 10, "head"), (384, 512, 520, 264, 5, 5, 0)])
+def test_chain_kchunk_one_gpu(case):
+    M, K, N1, N2, c1, c2, g = case
+    pl, X, W1, W2 = _kchunk_case(M, K, N1, N2, c1, c2, 0, 0, g)
+    mx, mean = oc.error_stats(pl.Y2.cpu(), oc.chain_reference(X, [W1, W2]))
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+def test_chain_kchunk_three_stages_one_gpu():
+    from ctapp.pipeline import Chain
+    M, K, widths = 512, 512, [768, 1024, 512]
+    ch = Chain(M, K, widths, [0, 0, 0], cfg=[10, 11, 10], group_rows=2, scoreboard="kchunk")
+    X, Ws = oc.make_chain_inputs(M, K, widths, seed=4)
+    for _ in range(2):
+        ch.run(X.cuda(), [w.cuda() for w in Ws])
+        ch.check()
+    mx, mean = oc.error_stats(ch.Y[-1].cpu(), oc.chain_reference(X, Ws))
+    assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+    assert all(int(c.min().item()) == 2 for c in ch.chunk[1:])
+
+
+def test_kchunk_consumer_without_producer_times_out_cleanly():
+    """Host-side fault injection: a consuming stage whose k-chunk flags nobody raises gives up (code 8) and the context lives on."""
+    from ctapp.ext import load, new_status
+    ext = load()
+    ext.set_wait_limit_ms(50)
+    try:
+        M, K, N = 256, 256, 512
+        X = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda"); W = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+        Y = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        entries = torch.arange(2, dtype=torch.int32, device="cuda")
+        head = torch.zeros(1, dtype=torch.int32, device="cuda"); tail = torch.full((1,), 2, dtype=torch.int32, device="cuda")
+        flags = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+        status = new_status("cuda")
+        ext.ctapp_gemm(X, W, Y, 10, entries, head, tail, None, None, None, None, None, None, 2, 0, 0, status=status, chunk_src=flags, chunk_kblocks=4,
+                       chunk_value=1)
+        torch.cuda.synchronize()
+        s = status.cpu().tolist()
+        assert s[0] == 8 and s[3] == 1, s
+        ext.gemm_tma(X, W, Y, 10)
+        torch.cuda.synchronize()
+    finally:
+        ext.set_wait_limit_ms(2000)
 
 
 def test_chain_three_stages_one_gpu():
@@ -150,6 +227,33 @@ def test_chain_two_gpus(case):
     if M <= 1024:
         mx, mean = oc.error_stats(pl.Y2.cpu(), oc.chain_reference(X, [W1, W2]))
         assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("case", [(4096, 8192, 8192, 8192, 10, 10, 4), (4096, 8192, 8192, 8192, 10, 11, 4), (8192, 8192, 8192, 8192, 11, 11, 8),
+                                  (1024, 8192, 8192, 8192, 10, 10, 2)])
+def test_chain_kchunk_two_gpus(case):
+    """Producer and consumer really overlap: the consumer's main loops stream behind the producer's tiles."""
+    M, K, N1, N2, c1, c2, g = case
+    pl, X, W1, W2 = _kchunk_case(M, K, N1, N2, c1, c2, 0, 1, g, runs=8)
+    if M <= 1024:
+        mx, mean = oc.error_stats(pl.Y2.cpu(), oc.chain_reference(X, [W1, W2]))
+        assert mx <= 2e-2 and mean <= 1e-3, (mx, mean)
+
+
+@pytest.mark.multigpu(2)
+def test_kchunk_negative_control_two_gpus():
+    """skip_wait makes the consumer ignore the k-chunk flags: it must then read rows that have not arrived."""
+    from ctapp.pipeline import Pipeline
+    M, K, N = 8192, 8192, 8192
+    pl = Pipeline(M, K, N, N, 10, 10, devA=0, devB=1, skip_wait=1, group_rows=4, scoreboard="kchunk")
+    X, (W1, W2) = oc.make_chain_inputs(M, K, [N, N], seed=0)
+    with torch.cuda.device(pl.b):
+        pl.Y1.fill_(float("nan"))
+    torch.cuda.synchronize(pl.b)
+    pl.run(X.to(pl.a), W1.to(pl.a), W2.to(pl.b))
+    pl.check()
+    assert torch.isnan(pl.Y2.float()).any(), "skipping the waits changed nothing: the test cannot see races"
 
 
 @pytest.mark.multigpu(2)

@@ -74,7 +74,7 @@ def test_consumer_pop_windows_are_a_permutation_in_n_major_order(tm, tn, g):
 
 
 def test_boundary_tail_rule_matches_oracle():
-    """``CtappBoundary._tail`` (host logic, no GPU needed for the rule itself) against the oracle's statement of it."""
+    """``CtappBoundary.tail_cols`` (host logic, no GPU needed for the rule itself) against the oracle's statement of it."""
     from oracle import boundary as ob
     import types
     from ctapp.tp4 import CtappBoundary
@@ -82,7 +82,7 @@ def test_boundary_tail_rule_matches_oracle():
         for raster, swz, down_tail in ((1, 1, "auto"), (2, 1, "auto"), (1, 2, "auto"), (1, 1, 5), (1, 1, 32)):
             fake = types.SimpleNamespace(down_tail=down_tail, down_raster=raster, down_swizzle=swz, n1=8192)
             want = down_tail if down_tail != "auto" else ob.tail_cols(M, raster, swz)
-            assert CtappBoundary._tail(fake, M) == want
+            assert CtappBoundary.tail_cols(fake, M) == want
 
 
 def test_gantt_svg_from_synthetic_stamps(tmp_path):

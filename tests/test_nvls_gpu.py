@@ -26,8 +26,8 @@ def test_nvls_probes():
     _run(mp_cases.nvls_probes, 29711)
 
 
-@pytest.mark.parametrize("protocol,fusion,cta_pair,red_variant", [("v5", "pdl", True, 3), ("v3", "pdl", True, 3), ("v3", "none", False, 1), ("v3", "pdl", True, 1)])
-def test_boundary_one_process_per_gpu(protocol, fusion, cta_pair, red_variant):
+@pytest.mark.parametrize("protocol,fusion,cta_pair,steal", [("v5", "pdl", True, 1), ("v3", "pdl1", True, 1), ("v3", "none", False, 0), ("v3", "pdl", True, 0)])
+def test_boundary_one_process_per_gpu(protocol, fusion, cta_pair, steal):
     import mp_cases
-    port = 29712 + ["v5", "v3"].index(protocol) * 4 + int(cta_pair) * 2 + (red_variant == 3)
-    _run(mp_cases.boundary_case, port, protocol, fusion, cta_pair, (1024, 256, 768, 1024), 2048, 8192, 2048, red_variant)
+    port = 29712 + ["v5", "v3"].index(protocol) * 4 + int(cta_pair) * 2 + steal
+    _run(mp_cases.boundary_case, port, protocol, fusion, cta_pair, (1024, 256, 768, 1024), 2048, 8192, 2048, bool(steal))

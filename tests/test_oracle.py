@@ -178,3 +178,35 @@ def test_chain_reference_small():
     assert mx <= 2e-2 and mean <= 5e-3
     X2, Ws2 = oc.make_chain_inputs(64, 128, [96, 80], seed=0)
     assert torch.equal(X, X2) and all(torch.equal(a, b) for a, b in zip(Ws, Ws2))
+
+
+def test_unit_map_orders_are_bijections_and_follow_the_producer():
+    """Every unit order visits each (panel, n-tile, quarter) once; the tail order is the producer's ``remap_tile`` restricted to
+    a rank's panels; order 2 is panel by panel; swizzle groups keep ``swz`` n-tiles together."""
+    for Pr, tn, tail, order, swz in ((4, 8, 0, 1, 1), (4, 8, 0, 1, 2), (4, 8, 0, 1, 4), (3, 6, 0, 2, 1), (5, 8, 3, 1, 1)):
+        units = [ob.unit_map(u, Pr, tn, tail, order, swz) for u in range(Pr * tn * 4)]
+        assert sorted(units) == [(j, n, q) for j in range(Pr) for n in range(tn) for q in range(4)]
+    assert [ob.unit_map(4 * t, 2, 4, 0, 1, 2)[:2] for t in range(8)] == [(0, 0), (0, 1), (1, 0), (1, 1), (0, 2), (0, 3), (1, 2), (1, 3)]
+    assert [ob.unit_map(4 * t, 2, 3, 0, 2)[:2] for t in range(6)] == [(0, 0), (0, 1), (0, 2), (1, 0), (1, 1), (1, 2)]
+    # tail order == the producer's order when one rank owns every panel
+    assert [ob.unit_map(4 * t, 4, 8, 3)[:2] for t in range(32)] == [ob.remap_tile(L, 4, 8, 3) for L in range(32)]
+
+
+def test_tile_orders_are_bijections():
+    for order, TM, TN, g, tail in ((0, 7, 5, 3, 0), (0, 4, 4, 8, 0), (1, 6, 8, 0, 3), (1, 6, 8, 0, 0), (2, 5, 3, 0, 0)):
+        tiles = ob.tile_order(order, TM, TN, g, tail)
+        assert sorted(tiles) == [(m, n) for m in range(TM) for n in range(TN)]
+    assert ob.tile_order(0, 3, 2, 2) == [(0, 0), (1, 0), (0, 1), (1, 1), (2, 0), (2, 1)]
+
+
+def test_kchunk_link_model():
+    """Flags all carry the run's number afterwards; a consumer tile can complete only after the LAST producer tile of its row
+    (in producer order) has finished, and a consumer walking the same grouped order as its producer never needs a tile from a
+    later group than its own."""
+    tm, tn1, tn2, g = 8, 4, 6, 2
+    o1, o2 = oc.producer_order(tm * tn1, tn1, g), oc.producer_order(tm * tn2, tn2, g)
+    flags, need = oc.simulate_kchunk_link(o1, tn1, o2, tn2, tn1, run_id=3)
+    assert flags.shape == (tm, tn1) and (flags == 3).all()
+    rows = o2 // tn2
+    assert (need <= (rows // g + 1) * g * tn1).all() and (need > (rows // g) * g * tn1).all()
+    assert (np.diff(need.reshape(-1, g * tn2).max(axis=1)) > 0).all()          # groups become ready in order

@@ -15,7 +15,11 @@ def test_knobs_defaults_and_validation():
     import ctapp_vllm
     k = ctapp_vllm.knobs({})
     assert k == {"enabled": False, "boundary": "both", "proto": "v5", "fusion": "pdl", "qkv_tile": 256, "max_M": 8192, "min_M": 512,
-                 "R": None, "check": False, "log_M": False, "steal": None}
+                 "R": None, "check": False, "log_M": False, "cksum": False, "steal_a": True, "steal_b": False,
+                 "a_raster": 3, "a_swizzle": 4, "b_raster": 2, "b_swizzle": 1}
+    k = ctapp_vllm.knobs({"CTAPP_STEAL": "0", "CTAPP_FUSION": "pdl1", "CTAPP_A_RASTER": "2", "CTAPP_B_SWIZZLE": "2", "CTAPP_CKSUM": "1"})
+    assert (k["steal_a"], k["steal_b"], k["fusion"], k["a_raster"], k["b_swizzle"], k["cksum"]) == (False, False, "pdl1", 2, 2, True)
+    assert ctapp_vllm.knobs({"CTAPP_STEAL": "1"})["steal_b"]
     k = ctapp_vllm.knobs({"CTAPP_VLLM": "1", "CTAPP_BOUNDARY": "down", "CTAPP_PROTO": "v3", "CTAPP_FUSION": "none", "CTAPP_QKV_TILE": "128",
                           "CTAPP_MAX_M": "16384", "CTAPP_MIN_M": "256", "CTAPP_R": "8", "CTAPP_CHECK": "1"})
     assert k["enabled"] and k["boundary"] == "down" and k["proto"] == "v3" and k["fusion"] == "none" and k["qkv_tile"] == 128

@@ -165,9 +165,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         }
         const uint32_t full0 = mapa_u32(full, 0);   // the leader's full[0] as a cluster address; stages are 8 bytes apart
         next = -2;
+        int chunk_upto = 0;   // k-chunks [0, chunk_upto) of this tile's rows are known to have landed
+        const int nchunks = p.chunk_src ? (KB + p.chunk_kblocks - 1) / p.chunk_kblocks : 0;
         for (int kb = 0; kb < KB; kb++) {
           // k-chunk dependencies: the flag covers the pair's 256 rows; each CTA asks for itself before it loads its half
-          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && !wait_chunk(p, mp, kb, limit)) { abort_pair(kStatusTimeoutChunk); ok = false; break; }
+          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && kb / p.chunk_kblocks >= chunk_upto) {
+            chunk_upto = wait_chunks(p, mp, kb / p.chunk_kblocks, nchunks, limit);
+            if (chunk_upto <= kb / p.chunk_kblocks) { abort_pair(kStatusTimeoutChunk); ok = false; break; }
+          }
           if (!mbar_wait(empty + stage, phase ^ 1, s_abort, limit)) { ok = false; break; }
           if (leader) mbar_arrive_expect_tx(full + stage, 2 * Cfg::kStageBytes);   // both CTAs' bytes are counted here
           tma_load_2d_pair(sA + stage * Cfg::kABytes, &p.tmA, kb * BK, m * BM, full0 + stage * 8);

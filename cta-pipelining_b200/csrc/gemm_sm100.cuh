@@ -79,16 +79,34 @@ struct alignas(64) GemmParams {
   ReduceParams red;                // tensor-parallel consumer: the owner reducer's arguments when its CTAs help (red.unit_ctr != null)
 };
 
-// Bounded wait of a consuming GEMM for one k-chunk of its A rows (written by the previous GPU's epilogue).
-__device__ __forceinline__ bool wait_chunk(const GemmParams& p, int m, int kb, long long limit) {
-  int seen;
-  const int idx = m * p.chunk_cols + kb / p.chunk_kblocks;
-  if (!spin_acquire_sys(p.chunk_src + idx, PredGe{p.chunk_value}, limit, seen)) {
-    report_status(p.status, kStatusTimeoutChunk, idx, p.chunk_value, seen);
-    return false;
+// Bounded wait of a consuming GEMM for k-chunk c of its A rows (written by the previous GPU's epilogue).  One call looks at up
+// to eight consecutive flags at once (independent relaxed loads, one acquire fence for all of them) and returns the first
+// chunk index that is NOT known to be ready, so that a tile whose row is already complete asks four times per 32 chunks, not 32
+// times; a return value <= c means the wait gave up (status written).
+__device__ __forceinline__ int wait_chunks(const GemmParams& p, int m, int c, int nchunks, long long limit) {
+  const int* row = p.chunk_src + m * p.chunk_cols;
+  const int look = min(8, nchunks - c);
+  unsigned long long t0 = 0;
+  unsigned polls = 0;
+  while (true) {
+    int v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = i < look ? ld_relaxed_sys(row + c + i) : 0;
+    int ready = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) ready += (ready == i && i < look && v[i] >= p.chunk_value) ? 1 : 0;
+    if (ready > 0) {
+      fence_acq_rel_sys();          // relaxed loads that saw the flags + this fence = acquire: the rows behind them are visible
+      fence_proxy_async_global();   // ... and to this GPU's async proxy, which does the loads
+      return c + ready;
+    }
+    if (polls == 0) t0 = globaltimer();
+    if (++polls > 16) __nanosleep(64);
+    if ((polls & 63u) == 0 && static_cast<long long>(globaltimer() - t0) > limit) {
+      report_status(p.status, kStatusTimeoutChunk, m * p.chunk_cols + c, p.chunk_value, v[0]);
+      return c;
+    }
   }
-  fence_proxy_async_global();   // the rows were written through another GPU's async proxy; the loads below go through this one's
-  return true;
 }
 
 // Chain mode: which slot of the source queue the idx-th pop reads.  The producer publishes a finished row panel as tiles_n
@@ -255,8 +273,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           if (m < 128) panel_seen[m >> 5] |= 1u << (m & 31);   // a panel flag never goes back within a launch: ask once
         }
         next = -2;
+        int chunk_upto = 0;   // k-chunks [0, chunk_upto) of this tile's rows are known to have landed
+        const int nchunks = p.chunk_src ? (KB + p.chunk_kblocks - 1) / p.chunk_kblocks : 0;
         for (int kb = 0; kb < KB; kb++) {
-          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && !wait_chunk(p, m, kb, limit)) { *s_abort = kStatusTimeoutChunk; ok = false; break; }
+          if (p.chunk_src && !p.skip_wait && kb % p.chunk_kblocks == 0 && kb / p.chunk_kblocks >= chunk_upto) {
+            chunk_upto = wait_chunks(p, m, kb / p.chunk_kblocks, nchunks, limit);
+            if (chunk_upto <= kb / p.chunk_kblocks) { *s_abort = kStatusTimeoutChunk; ok = false; break; }
+          }
           if (!mbar_wait(empty + stage, phase ^ 1, s_abort, limit)) { ok = false; break; }
           mbar_arrive_expect_tx(full + stage, Cfg::kStageBytes);
           tma_load_2d(sA + stage * Cfg::kABytes, &p.tmA, kb * BK, m * BM, full + stage);

@@ -1,6 +1,7 @@
 """2-layer chain on 2 GPUs, M sweep, gated latency: the CTA-pipelined chain against one GPU doing both layers (half of
 which is the ideal: one GEMM's time), micro-batching with peer copies (best chunk), and tensor parallelism with an NCCL
-all-reduce.  Mirrors reference bench/fig5.py:29-93.  One process drives both GPUs.
+all-reduce.  Mirrors reference bench/fig5.py:29-93.  One process drives both GPUs.  The chain is timed with the reference's
+row-panel scoreboard (``--groups``) and with k-chunk dependencies (``--kchunk``); the best of all is reported as ``ctapp_us``.
 
     python cta-pipelining_b200/bench/fig5.py [--ms 1024,2048,4096,8192,16384,32768] [--reps 20] [--out fig5.json]
 """
@@ -26,6 +27,8 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--cfg", type=int, default=10)
     ap.add_argument("--groups", default="1,2,4,ramp")
+    ap.add_argument("--kchunk", default="10:11:4,10:11:2,10:10:4", help="k-chunk variants producer_cfg:consumer_cfg:group_rows, comma separated ('' = none): "
+                    "the consumer's main loops stream behind the producer's tiles instead of waiting for whole row panels")
     ap.add_argument("--out", default=None)
     ap.add_argument("--skip-baselines", action="store_true", help="only the ideal, this library on one GPU and the pipelined chain")
     a = ap.parse_args()
@@ -62,6 +65,14 @@ def main():
             r[f"ctapp_g{gr}_us"] = t
             if bestc is None or t < bestc[0]:
                 bestc = (t, gr)
+        for var in [v for v in a.kchunk.split(",") if v]:
+            c1, c2, gr = (int(x) for x in var.split(":"))
+            c = mt.Ctapp(M, X, W1a, W2b, c1, c2, gr, scoreboard="kchunk")
+            t = measure(c, a.reps)[0]
+            c.pl.check()
+            r[f"ctapp_kchunk_{var}_us"] = t
+            if bestc is None or t < bestc[0]:
+                bestc = (t, f"kchunk {var}")
         r["ctapp_us"], r["ctapp_group_rows"] = bestc
         r["ctapp_over_ideal"] = r["ctapp_us"] / r["ideal_us"]
         if not a.skip_baselines:

@@ -301,7 +301,7 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
   p.ppo = a->panels_per_owner; p.tail = a->tail_cols;
   p.order = a->order ? a->order : 1; p.swz = a->swz;
   p.unit_ctr = a->unit_ctr; p.unit_log = a->unit_log; p.trace = a->trace; p.status = a->status;
-  p.pdl_trigger = a->pdl_trigger;
+  p.pdl_trigger = a->pdl_trigger; p.help_all = a->help_all;
   if (a->x_mc || a->rowss_mc || a->panel_flag_mc) {   // NVLS variant: all three multicast addresses or none
     ARG(a->x_mc && a->rowss_mc && a->panel_flag_mc, "the NVLS variant needs x_mc, rowss_mc and panel_flag_mc");
     ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
@@ -576,7 +576,7 @@ int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* str
       a->M, kNoAllocMaxM);
   // what this variant does not do is refused, not dropped: a caller that set one of these would get other behaviour than it asked for
   ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc, "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc must be NULL");
-  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL and pdl_trigger 0");
+  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger and help_all 0");
   ReduceParams p;
   if (int r = fill_reduce(a, p, false)) return r;
   ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
   if constexpr (!kWide) {   // the wide tile is never a tensor-parallel consumer
-    if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch);   // every warp, before it takes up its role
+    if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);   // every warp, before it takes up its role
   }
 
   // a give-up in one CTA stops both

@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (p.pdl_trigger) pdl_launch_dependents();
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
-  if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch);   // every warp, before it takes up its role
+  if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);   // every warp, before it takes up its role
 
   if (warp == 0) {
     // ============================================================ scheduler + TMA loader

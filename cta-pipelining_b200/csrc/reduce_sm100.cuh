@@ -32,6 +32,7 @@ struct ReduceParams {
   int* status;
   long long limit_ns;
   int pdl_trigger;           // raise the programmatic-launch trigger at entry (the producer GEMM is this kernel's dependent)
+  int help_all;              // helpers (consumer CTAs): 1 = take every unit, waiting for tiles (no dedicated reducer CTAs run)
   // NVLS variant: multicast addresses of the x buffer, the row-sum buffer and the panel flags (null = unicast pushes)
   uint4* x_mc;
   float* rowss_mc;
@@ -214,13 +215,25 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
 
 // The unit loop of one warp.  Static assignment: unit = first, first + stride, ...; with p.unit_ctr every warp claims its
 // next unit from the shared counter instead (first / stride unused), which lets CTAs of another kernel join in.
-template <int W, int ROWS, bool MC>
+// kOnlyReady (helpers from another kernel): a warp takes a unit only while the NEXT unclaimed unit's tile has already arrived,
+// i.e. while the dedicated reducer CTAs are behind the producers; once the reducers keep pace it leaves instead of waiting.
+template <int W, int ROWS, bool MC, bool kOnlyReady = false>
 __device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, int first, int stride, int lane) {
   const int P = p.M / 128;
   const int Pr = P > p.rank ? (P - 1 - p.rank) / W + 1 : 0;
   const int tiles_n = p.n1 / 256;
   const int U = Pr * tiles_n * 4;
   auto claim = [&]() -> int {
+    if (kOnlyReady) {
+      int next = 0;
+      if (lane == 0) next = ld_relaxed_gpu(p.unit_ctr);
+      next = __shfl_sync(0xffffffffu, next, 0);
+      if (next >= U) return U;
+      int j, n, q;
+      unit_map(next, Pr, tiles_n, p.tail, p.order, p.swz, j, n, q);
+      const bool up = lane >= W || ld_relaxed_sys(p.tile_flags + (lane * p.ppo + j) * tiles_n + n) >= epoch;
+      if (!__all_sync(0xffffffffu, up)) return U;
+    }
     int v = 0;
     if (lane == 0) v = atomicAdd(p.unit_ctr, 1);
     return __shfl_sync(0xffffffffu, v, 0);
@@ -242,17 +255,25 @@ __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p
   reduce_units<W, ROWS, MC>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x) * nwarps, lane);
 }
 
-// Consumer CTAs helping the owner reducer (any CTA shape): every warp claims units until none are left.
-__device__ __forceinline__ void reduce_help(const ReduceParams& p, int epoch) {
+// Consumer CTAs helping the owner reducer (any CTA shape): every warp claims units while there are units whose tiles have
+// arrived and that nobody has taken (`all`: until no unit is left at all, waiting for tiles where necessary: for a launch without
+// dedicated reducer CTAs).
+__device__ __forceinline__ void reduce_help(const ReduceParams& p, int epoch, bool all) {
   const int lane = threadIdx.x & 31;
   if (!p.unit_ctr) return;
   const bool mc = p.x_mc != nullptr;
+#define CTAPP_HELP(W, R)                                                                                          \
+  do {                                                                                                              \
+    if (all) { if (mc) reduce_units<W, R, true, false>(p, epoch, 0, 0, lane); else reduce_units<W, R, false, false>(p, epoch, 0, 0, lane); } \
+    else { if (mc) reduce_units<W, R, true, true>(p, epoch, 0, 0, lane); else reduce_units<W, R, false, true>(p, epoch, 0, 0, lane); }     \
+  } while (0)
   switch (p.world) {
-    case 1: reduce_units<1, 4, false>(p, epoch, 0, 0, lane); break;
-    case 2: if (mc) reduce_units<2, 2, true>(p, epoch, 0, 0, lane); else reduce_units<2, 2, false>(p, epoch, 0, 0, lane); break;
-    case 4: if (mc) reduce_units<4, 2, true>(p, epoch, 0, 0, lane); else reduce_units<4, 2, false>(p, epoch, 0, 0, lane); break;
-    default: if (mc) reduce_units<8, 1, true>(p, epoch, 0, 0, lane); else reduce_units<8, 1, false>(p, epoch, 0, 0, lane); break;
+    case 1: if (all) reduce_units<1, 4, false, false>(p, epoch, 0, 0, lane); else reduce_units<1, 4, false, true>(p, epoch, 0, 0, lane); break;
+    case 2: CTAPP_HELP(2, 2); break;
+    case 4: CTAPP_HELP(4, 2); break;
+    default: CTAPP_HELP(8, 1); break;
   }
+#undef CTAPP_HELP
 }
 
 // Read-back of the unit order: out[3 u .. 3 u + 2] = (j, n, q) for every unit of a rank with Pr owned panels.

@@ -108,7 +108,7 @@ class TpReduceArgs(C.Structure):
                 ("resid", C.c_void_p), ("peer_x", C.c_void_p * MAX_WORLD), ("peer_rowss", C.c_void_p * MAX_WORLD),
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("order", C.c_int), ("swz", C.c_int), ("unit_ctr", C.c_void_p),
-                ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("trace", C.c_void_p),
+                ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("help_all", C.c_int), ("trace", C.c_void_p),
                 ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p)]
 
 
@@ -407,7 +407,7 @@ class Tp4Module:
     @staticmethod
     def _reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                      rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=1, swz=1, unit_ctr=0, unit_log=None, pdl_trigger=0,
-                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
+                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0):
         """The owner reducer's argument block (``ctapp_tp_reduce_args``), shared by tp4_reduce, tp4_reduce_noalloc and the mode-8
         consumer.  ``panels_per_owner`` is required: the flags are indexed with it, and a wrong value aliases the sources."""
         if panels_per_owner <= 0:
@@ -421,7 +421,7 @@ class Tp4Module:
         a.resid = _ptr(resid)
         a.rowss_local, a.panel_done = _ptr(rowss_local), _ptr(panel_done)
         a.panels_per_owner, a.tail_cols, a.order, a.swz = int(panels_per_owner), int(tail_cols), int(order), int(swz)
-        a.unit_ctr, a.unit_log, a.pdl_trigger = _ptr(unit_ctr), _ptr(unit_log), int(pdl_trigger)
+        a.unit_ctr, a.unit_log, a.pdl_trigger, a.help_all = _ptr(unit_ctr), _ptr(unit_log), int(pdl_trigger), int(help_all)
         a.trace, a.status = _ptr(red_trace), _ptr(status)
         a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
         return a
@@ -429,7 +429,7 @@ class Tp4Module:
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
                 tile=256, R=0, role_ctr=None, rank=0, red_order=1, red_swz=1, tile_flags=None, resid=None, inbox_ptrs=(), peer_x=(),
                 peer_rowss=(), peer_panel_flag=(), rowss_local=0, panel_done=0, panels_per_owner=0, red_rows=4, trace=0, red_trace=0,
-                red_stages=0, red_dyn=0, red_tail=0, status=None, eps=1e-5, cta_pair=0, act=0, world=1, unit_ctr=None,
+                red_stages=0, red_dyn=0, red_tail=0, status=None, eps=1e-5, cta_pair=0, act=0, world=1, unit_ctr=None, help_all=0,
                 x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
         """Modes 0 (plain, optional row scaling), 5 (per-panel waits) and 8: as 5, and every CTA first helps the owner reducer by
         claiming units from ``unit_ctr`` (default ``role_ctr[1:]``), for which the reducer's arguments (``rank`` .. ``red_tail``,
@@ -457,7 +457,7 @@ class Tp4Module:
             red = self._reduce_args(a.M, rank, world, epoch, epoch_dev, 1, 32, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                                     rowss_local, panel_done, panels_per_owner, red_tail, a.K, status, order=red_order, swz=red_swz,
                                     unit_ctr=unit_ctr, red_trace=red_trace, x_mc_ptr=x_mc_ptr, rowss_mc_ptr=rowss_mc_ptr,
-                                    panel_flag_mc_ptr=panel_flag_mc_ptr)
+                                    panel_flag_mc_ptr=panel_flag_mc_ptr, help_all=help_all)
             a.red = C.cast(C.pointer(red), C.c_void_p)
         dev = X.device.index
         _check(self.lib.ctapp_tp_qkv(C.byref(a), dev, _stream(dev)))

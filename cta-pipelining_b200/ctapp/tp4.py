@@ -196,7 +196,9 @@ class CtappBoundary:
             "serial" = step, producer, reducer, consumer on one stream, nothing concurrent on this GPU (used where a
                      single GPU plays every rank).
     steal: the consumer runs in mode 8: each of its CTAs first claims owner-reducer units from the counter the dedicated
-    reducer CTAs claim from, so CTAs that become resident as the producer's retire drain what the reducer has not reached
+    reducer CTAs claim from, as long as there are units whose tiles have arrived and that no reducer warp has taken yet, so CTAs
+    that become resident as the producer's retire drain what the reducer has fallen behind by, and start their own tiles at
+    once when the reducer keeps pace
     (reference ctapp/tp4.py:110-114, csrc/ctapp_tp4.cuh:913-925).  ``R=0`` with steal leaves the reduction to them alone
     (with fusion "serial" that only works for world 1: a consumer that reduces its own panels and then waits for the other
     ranks' panels needs those ranks' consumers to run at the same time).
@@ -326,7 +328,8 @@ class CtappBoundary:
             return
         self.ext.tp4_qkv(*args, 8, 0, self.buf.panel_flag, 1, self.buf.rowss[parity], role_ctr=self.buf.role_ctr, rank=self.rank,
                          world=self.world, red_order=2 if self.down_raster == 2 else 1, red_swz=self.down_swizzle,
-                         tile_flags=self.buf.tile_flags, red_tail=self.tail_cols(M), **self._reducer_kwargs(M, resid, parity), **common)
+                         tile_flags=self.buf.tile_flags, red_tail=self.tail_cols(M), help_all=int(self.red_blocks == 0),
+                         **self._reducer_kwargs(M, resid, parity), **common)
 
     # ---- how the kernels of one step are put on streams
     def _step(self, M):

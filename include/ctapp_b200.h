@@ -193,6 +193,10 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
                                                (j << 16 | n << 2 | q) per unit in the order the warps take them */
   int pdl_trigger;                          /* 1: raise the programmatic-launch trigger at entry, so that a producer GEMM
                                                launched behind this kernel with pdl = 1 starts beside it (ctapp/tp4.py:316-320) */
+  int help_all;                             /* only read through ctapp_tp_qkv mode 8: 0 = a helping warp takes a unit only while
+                                               the next unclaimed unit's tile has already arrived (the dedicated reducer CTAs are
+                                               behind the producers) and otherwise goes on to its GEMM tiles; 1 = helpers take
+                                               every unit and wait for tiles (no dedicated reducer CTAs are launched) */
   unsigned long long* trace;
   int* status;
   /* NVLS variant (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.st / multimem.red pushes): multicast addresses of the x

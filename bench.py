@@ -614,7 +614,7 @@ def main():
     ROWS = 256
     y_rows = (chain.Y[0] if world == 1 else stage.Yout)[:ROWS].cpu() if rank == n - 1 else torch.empty(ROWS, NK, dtype=torch.bfloat16)
     if world > 1:
-        yb = y_rows.view(torch.int16)
+        yb = y_rows.contiguous().view(torch.int32)      # raw bits: the side group's backend has no bf16
         dist.broadcast(yb, src=n - 1, group=gloo)
         y_rows = yb.view(torch.bfloat16)
     oracle_check = None

@@ -79,34 +79,19 @@ struct alignas(64) GemmParams {
   ReduceParams red;                // tensor-parallel consumer: the owner reducer's arguments when its CTAs help (red.unit_ctr != null)
 };
 
-// Bounded wait of a consuming GEMM for k-chunk c of its A rows (written by the previous GPU's epilogue).  One call looks at up
-// to eight consecutive flags at once (independent relaxed loads, one acquire fence for all of them) and returns the first
-// chunk index that is NOT known to be ready, so that a tile whose row is already complete asks four times per 32 chunks, not 32
-// times; a return value <= c means the wait gave up (status written).
+// Bounded wait of a consuming GEMM for k-chunk c of its A rows (written by the previous GPU's epilogue): one acquiring load
+// when the chunk is there already.  Returns the first chunk index not known to be ready (c + 1), or c when the wait gave up
+// (status written).  (Looking at several flags per poll with relaxed loads and one acquire fence for all of them measured
+// 9-12 % slower over a whole chain run than one acquiring load per chunk.)
 __device__ __forceinline__ int wait_chunks(const GemmParams& p, int m, int c, int nchunks, long long limit) {
-  const int* row = p.chunk_src + m * p.chunk_cols;
-  const int look = min(8, nchunks - c);
-  unsigned long long t0 = 0;
-  unsigned polls = 0;
-  while (true) {
-    int v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = i < look ? ld_relaxed_sys(row + c + i) : 0;
-    int ready = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) ready += (ready == i && i < look && v[i] >= p.chunk_value) ? 1 : 0;
-    if (ready > 0) {
-      fence_acq_rel_sys();          // relaxed loads that saw the flags + this fence = acquire: the rows behind them are visible
-      fence_proxy_async_global();   // ... and to this GPU's async proxy, which does the loads
-      return c + ready;
-    }
-    if (polls == 0) t0 = globaltimer();
-    if (++polls > 16) __nanosleep(64);
-    if ((polls & 63u) == 0 && static_cast<long long>(globaltimer() - t0) > limit) {
-      report_status(p.status, kStatusTimeoutChunk, m * p.chunk_cols + c, p.chunk_value, v[0]);
-      return c;
-    }
+  int seen;
+  const int idx = m * p.chunk_cols + c;
+  if (!spin_acquire_sys(p.chunk_src + idx, PredGe{p.chunk_value}, limit, seen)) {
+    report_status(p.status, kStatusTimeoutChunk, idx, p.chunk_value, seen);
+    return c;
   }
+  fence_proxy_async_global();   // the rows were written through another GPU's async proxy; the loads below go through this one's
+  return c + 1;
 }
 
 // Chain mode: which slot of the source queue the idx-th pop reads.  The producer publishes a finished row panel as tiles_n

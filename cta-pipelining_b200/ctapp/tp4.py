@@ -228,10 +228,13 @@ class CtappBoundary:
         # SM split: R SMs are left to the owner reducer (measured on B200 at M=4096: TP2 best with 4, TP4 and TP8 with 8)
         self.nsm = torch.cuda.get_device_properties(self.dev).multi_processor_count
         self.R = (8 if world >= 4 else 4) if R is None else int(R)
-        if self.R == 0 and not self.steal:
-            raise ValueError("R=0 (no dedicated reducer CTAs) needs steal=True")
+        # R = 0 gives both GEMMs every SM.  The reduction is then done by ``red_blocks`` small reducer CTAs that share SMs with
+        # the GEMMs' CTAs (a GEMM CTA leaves more than half of an SM's registers and nearly all its thread slots free; choose
+        # ``red_threads`` <= 512 so that both fit), by the consumer's CTAs (``steal``), or by both
+        if self.R == 0 and not self.steal and not red_blocks:
+            raise ValueError("R=0 (no SMs set aside for the reducer) needs red_blocks (reducer CTAs sharing SMs with the GEMMs) or steal=True")
         self.sms = self.qkv_sms = self.nsm - self.R
-        self.red_threads, self.red_blocks = red_threads, red_blocks or self.R
+        self.red_threads, self.red_blocks = red_threads, self.R if red_blocks is None else int(red_blocks)
         # tile orders of the three kernels
         self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
         self.down_raster, self.down_swizzle, self.down_tail = down_raster or 1, down_swizzle, down_tail

@@ -230,7 +230,8 @@ def test_add_rmsnorm_baseline_kernel():
 
 
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (False, {}), (True, dict(steal=True)), (True, dict(steal=True, R=0)), (False, dict(steal=True))])
+@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (False, {}), (True, dict(steal=True)), (True, dict(steal=True, R=0)), (False, dict(steal=True)),
+                                         (True, dict(R=0, red_blocks=48, red_threads=256))])     # last: reducer CTAs share SMs with the GEMMs' CTAs
 @pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl"), (2, "pdl1")])
 def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, kw):
     """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""

@@ -479,10 +479,11 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
   ARG(a->mode == 0 || a->mode == 7, "tp_down mode %d is not supported (0 | 7)", a->mode);
   ARG(a->world >= 1 && a->world <= CTAPP_MAX_WORLD && a->rank >= 0 && a->rank < a->world, "bad rank %d / world %d", a->rank, a->world);
   GUARD(device);
-  const bool pair = a->cta_pair != 0;
+  const bool pair = a->cta_pair != 0, wide = a->cta_pair == 2;     // 2: CTA pairs on 256 x 512 tiles (two tile flags per tile)
+  ARG(a->cta_pair >= 0 && a->cta_pair <= 2, "bad cta_pair %d", a->cta_pair);
   GemmParams p;
-  if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, 256, pair)) return r;
-  ARG(a->N % 256 == 0, "N=%d must be a multiple of 256", a->N);
+  if (int r = fill_common(p, a->A, a->W, a->M, a->N, a->K, wide ? 512 : 256, pair)) return r;
+  ARG(a->N % (wide ? 512 : 256) == 0, "N=%d must be a multiple of %d", a->N, wide ? 512 : 256);
   p.status = a->status; p.stamps = a->trace; p.tile_log = a->tile_log;
   // mode 7 launched as a programmatic dependent follows the owner reducer, which waits for THIS kernel's tiles: it must not
   // wait for that grid to finish (the step kernel before the reducer has completed by then: stream order)
@@ -490,8 +491,8 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
   p.epoch = a->epoch; p.epoch_ptr = a->epoch_dev;
   if (a->raster == 2) p.order = kOrderNFast;
   else {
-    ARG(a->tail_cols >= 0 && a->tail_cols <= p.tiles_n, "bad tail_cols %d", a->tail_cols);
-    p.order = kOrderMFastTail; p.tail_cols = a->tail_cols;
+    ARG(a->tail_cols >= 0 && a->tail_cols <= a->N / 256, "bad tail_cols %d", a->tail_cols);
+    p.order = kOrderMFastTail; p.tail_cols = wide ? a->tail_cols / 2 : a->tail_cols;      // tail_cols counts 256-column tiles
   }
   if (a->mode == 0) {
     ARG(a->D, "mode 0 needs D");
@@ -511,7 +512,7 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
       p.peer_tile_flags[d] = a->peer_tile_flags[d];
     }
   }
-  if (pair) return launch_gemm2(p, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
+  if (pair) return launch_gemm2(p, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream), wide);
   return launch_gemm(p, 256, a->sms, a->pdl, device, static_cast<cudaStream_t>(stream));
 }
 

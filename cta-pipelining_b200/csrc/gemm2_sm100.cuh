@@ -365,7 +365,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           epi_phase ^= 1;
           fence_acq_rel_sys();
           if (p.mode == kModeTpProducer) {
-            if (lane == 0) st_relaxed_sys(p.peer_tile_flags[dst] + (p.rank * p.ppo + m / p.world) * p.tiles_n + n, epoch);
+            // the owners index their tile flags in 256-column tiles: a 512-column tile raises two of them
+            constexpr int kFlags = BN / 256;
+            if (lane < kFlags) st_relaxed_sys(p.peer_tile_flags[dst] + (p.rank * p.ppo + m / p.world) * (kFlags * p.tiles_n) + kFlags * n + lane, epoch);
           } else if (!leader) {
             if (lane == 0) red_add_release_cluster(mapa_u32(s_peer_done, 0), 1);   // this half of the pair tile has landed
           } else {

@@ -207,7 +207,8 @@ class CtappBoundary:
     act: the consumer's weight is a gate/up projection with rows interleaved by ``interleave_gate_up``; its epilogue applies
     silu(gate) * up and ``out`` is (M, N2r / 2): the activation costs no pass over memory of its own.
     cta_pair: both GEMMs run as CTA pairs (``cta_group::2``, 256-row tiles; the protocol's unit stays the 128-row panel);
-    False = one CTA per 128-row tile.
+    "wide" = as True, and the producer works on 256 x 512 tiles (it raises two tile flags per tile); False = one CTA per
+    128-row tile.
     ``group_name``: a torch.distributed group name (one process per GPU) or a ``ctapp.symm.LocalGroup`` (one process
     drives every rank's GPU).
     """
@@ -222,6 +223,7 @@ class CtappBoundary:
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
         self.M, self.max_M, self.Kr, self.N2r, self.rank, self.world, self.group = M, max_M, Kr, N2r, rank, world, group_name
         self.n1, self.eps, self.cta_pair, self.act = n1, eps, int(bool(cta_pair)), int(bool(act))
+        self.down_pair = 2 if cta_pair == "wide" and n1 % 512 == 0 else self.cta_pair      # producer tile: 256 x 512 per CTA pair
         self.use_resid, self.protocol, self.v5 = resid, bool(protocol), bool(protocol)
         self.use_graph, self.graph_bind = use_graph, bool(graph_bind)
         self.fusion, self.steal = fusion, bool(steal)
@@ -319,7 +321,7 @@ class CtappBoundary:
         self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms if sms is None else sms,
                           epoch_dev=self.buf.epoch_dev, dst_ptrs=t["dst_ptrs"], dst_rows=self.ppo * 128, peer_tile_flags=t["peer_tf"],
                           panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, pdl=int(self.fusion == "pdl1"),
-                          trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.cta_pair,
+                          trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.down_pair,
                           tile_log=tile_log)
 
     def launch_consumer(self, Wq, M, parity, resid=None):
@@ -369,7 +371,7 @@ class CtappBoundary:
         if self._floor_y is None:
             self._floor_y = torch.empty(self.max_M, self.n1, dtype=DTYPE, device=self.dev)
         self.ext.tp4_down(h_r, Wd, self._floor_y[:M], self.down_raster, self.down_swizzle, 0, self.rank, self.world, 0, sms=self.sms,
-                          tail_cols=self.tail_cols(M), cta_pair=self.cta_pair)
+                          tail_cols=self.tail_cols(M), cta_pair=self.down_pair)
         self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile,
                          cta_pair=self.cta_pair, act=self.act)
 

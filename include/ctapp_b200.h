@@ -137,7 +137,9 @@ typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0
   int sms, pdl_trigger, pdl, tail_cols;
   unsigned long long* trace;
   int* status;
-  int cta_pair;                            /* 1 = two CTAs per 256-row tile (cta_group::2), 0 = one CTA per 128-row tile */
+  int cta_pair;                            /* 0 = one CTA per 128-row tile; 1 = two CTAs per 256-row tile (cta_group::2), 256
+                                              columns wide; 2 = the same on 256 x 512 tiles (N % 512 == 0; a tile raises the two
+                                              256-column tile flags it covers; a quarter less operand traffic per FLOP) */
   int* tile_log;                           /* NULL, or [0] = 0 on entry and room for 1 + #tiles ints: the kernel appends one packed
                                               (m << 16 | n) per tile in the order its schedulers take them (m = tile row of the
                                               schedule: 256 rows with cta_pair); with one CTA (pair) that is the tile order itself */

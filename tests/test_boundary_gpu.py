@@ -74,7 +74,8 @@ def _forward_and_check(bds, M, K, n1, N2_, seed, use_resid=True, out_ulp=0.98):
         assert int(bd.epoch_dev.item()) == bd.epoch
 
 
-@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (True, dict(steal=True)), (False, dict(down_raster=2)), (False, dict(steal=True, down_tail=0))])
+@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (True, dict(steal=True)), (False, dict(down_raster=2)), (False, dict(steal=True, down_tail=0)),
+                                         ("wide", {}), ("wide", dict(down_tail=1))])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_boundary_one_gpu_plays_all_ranks(world, cta_pair, kw):
     """``steal`` here: the dedicated reducers claim their units from the shared counter and the mode-8 consumers, launched after

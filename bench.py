@@ -271,9 +271,11 @@ def latency_record(M_list, cfg, reps=10):
             t = measure(mt.MicroBatchCublas(M, X, W1a, W2b, chunk), reps)[0]
             best = (t, chunk) if best is None or t < best[0] else best
         r["microbatch_cublas_us"], r["microbatch_chunk"] = best
-        for name, kw in (("rowpanel_g2", dict(group_rows=2)), ("kchunk_g4", dict(group_rows=4, scoreboard="kchunk")),
-                         ("kchunk_g8", dict(group_rows=8, scoreboard="kchunk"))):
-            c = mt.Ctapp(M, X, W1a, W2b, cfg, cfg, kw["group_rows"], scoreboard=kw.get("scoreboard", "rowpanel"))
+        # the reference's row-panel scoreboard at its best group size, and k-chunk dependencies with the consumer on the
+        # 256 x 512 tile (one acquiring poll per 3.1 us of tensor work; on the 256 x 256 tile the polls starve the loader)
+        for name, kw in (("rowpanel_g2", dict(group_rows=2)), ("kchunk_wide_consumer_g4", dict(group_rows=4, scoreboard="kchunk", cfg_c=GEMM_CFG_WIDE)),
+                         ("kchunk_wide_consumer_g3", dict(group_rows=3, scoreboard="kchunk", cfg_c=GEMM_CFG_WIDE))):
+            c = mt.Ctapp(M, X, W1a, W2b, cfg, kw.get("cfg_c", cfg), kw["group_rows"], scoreboard=kw.get("scoreboard", "rowpanel"))
             r[f"chain_{name}_us"] = measure(c, reps)[0]
             c.pl.check()
             del c

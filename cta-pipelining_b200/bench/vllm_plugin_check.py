@@ -86,6 +86,7 @@ def worker(rank, world, port, cfg_dir, tokens, results):
             h0, top0 = run(stock)
             del stock
             torch.cuda.empty_cache()
+            vcfg.compilation_config.static_forward_context.clear()      # the attention layers register themselves by name: start afresh
             os.environ.update({"CTAPP_VLLM": "1", "CTAPP_CHECK": "1", "CTAPP_MIN_M": "128"})
             import ctapp_vllm
             ctapp_vllm.register()

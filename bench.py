@@ -198,11 +198,11 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     steal = bool(args.steal) if args.steal in (0, 1) else t >= 8
     bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion,
                            R=None if args.R < 0 else args.R, steal=steal, red_blocks=args.red_blocks if args.red_blocks >= 0 else None,
-                           red_threads=args.red_threads, cta_pair="wide" if args.down_wide else True, **akw)
+                           red_threads=args.red_threads, cta_pair={1: "wide", 0: "narrow"}.get(args.down_wide, True), **akw)
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
-    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=bd.R, red_blocks=1, cta_pair="wide" if args.down_wide else True, **akw)
+    fl = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=False, max_M=M, R=bd.R, red_blocks=1, cta_pair={1: "wide", 0: "narrow"}.get(args.down_wide, True), **akw)
     res["two_gemm_floor"] = tp4.time_step(lambda: fl.forward(h_r, None, Wd_r, Wqf_r), dev, iters, warm)
     st = tp4.NcclFusedNormBoundary(M, rank, t, None, dev, Wd_r, Wq_r, gamma)
     res["cublas_nccl_fusednorm"] = tp4.time_step(lambda: st.forward(h_r, resid), dev, iters, warm)
@@ -233,7 +233,7 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     burst, sustained, kind = peaks()
     b2b = res["ctapp"][1]
     return {"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
-            "n_gpus": t, "fusion": args.fusion, "steal": steal, "R": bd.R, "red_blocks": bd.red_blocks, "red_threads": bd.red_threads, "producer_tile": "256x512" if bd.down_pair == 2 else "256x256", "push": "nvls multimem" if bd.nvls else "unicast",
+            "n_gpus": t, "fusion": args.fusion, "steal": steal, "R": bd.R, "red_blocks": bd.red_blocks, "red_threads": bd.red_threads, "producer_tile": "256x512" if bd.down_pair(M) == 2 else "256x256", "push": "nvls multimem" if bd.nvls else "unicast",
             "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
             "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
             "over_two_gemm_floor_b2b": b2b / res["two_gemm_floor"][1],
@@ -420,7 +420,7 @@ def main():
                     "three: steps overlap, so the fill is paid once per run and per link; on 2 GPUs 'head' measured 0.7-0.9 %% slower than 8)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
     ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = on at TP8 only: it measured neutral to slightly slower at TP2 and TP4")
-    ap.add_argument("--down-wide", type=int, default=0, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles")
+    ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")
     ap.add_argument("--red-blocks", type=int, default=-1, help="boundary: reducer CTAs (-1 = R; with --R 0 they share SMs with the GEMMs' CTAs)")
     ap.add_argument("--red-threads", type=int, default=1024, help="boundary: threads per reducer CTA (<= 512 to share an SM with a GEMM CTA)")
     ap.add_argument("--no-sustained", action="store_true", help="chain: keep the one-second sustained loop as short as the timed region (profiler captures)")

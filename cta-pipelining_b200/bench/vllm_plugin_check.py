@@ -90,6 +90,10 @@ def worker(rank, world, port, cfg_dir, tokens, results):
             os.environ.update({"CTAPP_VLLM": "1", "CTAPP_CHECK": "1", "CTAPP_MIN_M": "128"})
             import ctapp_vllm
             ctapp_vllm.register()
+            # vLLM remembers which class an architecture resolved to; a serving process registers the plugin before anything
+            # is resolved, this process resolved the stock class a moment ago
+            from vllm.model_executor.model_loader import utils as loader_utils
+            getattr(loader_utils, "_MODEL_ARCH_BY_HASH", {}).clear()
             ours = get_model(vllm_config=vcfg)
             out["plugin_class"] = type(ours).__name__
             h1, top1 = run(ours)                 # first forward: folds the norm weights, creates both boundaries (collective)

@@ -207,8 +207,8 @@ class CtappBoundary:
     act: the consumer's weight is a gate/up projection with rows interleaved by ``interleave_gate_up``; its epilogue applies
     silu(gate) * up and ``out`` is (M, N2r / 2): the activation costs no pass over memory of its own.
     cta_pair: both GEMMs run as CTA pairs (``cta_group::2``, 256-row tiles; the protocol's unit stays the 128-row panel);
-    "wide" = as True, and the producer works on 256 x 512 tiles (it raises two tile flags per tile); False = one CTA per
-    128-row tile.
+    the producer then works on 256 x 512 tiles (raising two tile flags per tile) when M is large enough to give every pair
+    such a tile, on 256 x 256 tiles otherwise; "wide" / "narrow" force either; False = one CTA per 128-row tile.
     ``group_name``: a torch.distributed group name (one process per GPU) or a ``ctapp.symm.LocalGroup`` (one process
     drives every rank's GPU).
     """
@@ -223,7 +223,9 @@ class CtappBoundary:
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
         self.M, self.max_M, self.Kr, self.N2r, self.rank, self.world, self.group = M, max_M, Kr, N2r, rank, world, group_name
         self.n1, self.eps, self.cta_pair, self.act = n1, eps, int(bool(cta_pair)), int(bool(act))
-        self.down_pair = 2 if cta_pair == "wide" and n1 % 512 == 0 else self.cta_pair      # producer tile: 256 x 512 per CTA pair
+        # producer tile: CTA pairs work on 256 x 512 tiles (a quarter less operand traffic; TP2, M=4096: 0.921 against 0.938 ms
+        # for the whole boundary) whenever that still gives every pair a tile; "wide" / "narrow" force the choice
+        self._down_wide = {"wide": True, "narrow": False}.get(cta_pair) if isinstance(cta_pair, str) else (None if cta_pair else False)
         self.use_resid, self.protocol, self.v5 = resid, bool(protocol), bool(protocol)
         self.use_graph, self.graph_bind = use_graph, bool(graph_bind)
         self.fusion, self.steal = fusion, bool(steal)
@@ -297,6 +299,15 @@ class CtappBoundary:
             return 0
         return min(16 if M >= 2048 else 8, self.n1 // 256)
 
+    def down_pair(self, M):
+        """``cta_pair`` value of the producer launch for M rows: 0 one CTA per tile, 1 CTA pairs on 256 x 256, 2 on 256 x 512."""
+        if not self.cta_pair or self.n1 % 512:
+            return self.cta_pair
+        wide = self._down_wide
+        if wide is None:
+            wide = (M // 256) * (self.n1 // 512) >= self.sms // 2
+        return 2 if wide else 1
+
     def _stamps(self, t):
         return t.data_ptr() if self.trace else 0
 
@@ -321,7 +332,7 @@ class CtappBoundary:
         self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms if sms is None else sms,
                           epoch_dev=self.buf.epoch_dev, dst_ptrs=t["dst_ptrs"], dst_rows=self.ppo * 128, peer_tile_flags=t["peer_tf"],
                           panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, pdl=int(self.fusion == "pdl1"),
-                          trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.down_pair,
+                          trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.down_pair(M),
                           tile_log=tile_log)
 
     def launch_consumer(self, Wq, M, parity, resid=None):
@@ -371,7 +382,7 @@ class CtappBoundary:
         if self._floor_y is None:
             self._floor_y = torch.empty(self.max_M, self.n1, dtype=DTYPE, device=self.dev)
         self.ext.tp4_down(h_r, Wd, self._floor_y[:M], self.down_raster, self.down_swizzle, 0, self.rank, self.world, 0, sms=self.sms,
-                          tail_cols=self.tail_cols(M), cta_pair=self.down_pair)
+                          tail_cols=self.tail_cols(M), cta_pair=self.down_pair(M))
         self.ext.tp4_qkv(self._floor_y[:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle, 0, 0, sms=self.qkv_sms, tile=self.qkv_tile,
                          cta_pair=self.cta_pair, act=self.act)
 

@@ -198,6 +198,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
               while (!mbar_try_wait_cluster(full + s, (armed_parity >> s) & 1u) && globaltimer() - t0 < 2000000ull) {}
             }
         } else {
+          // This CTA's loads complete on the LEADER's barriers, which it cannot wait on for itself.  Loads of stages the leader
+          // armed are covered by the leader's wait above: this CTA stays resident until the closing cluster barrier, which the
+          // leader reaches only after that wait.  For a stage this CTA loaded but the leader never armed (the leader gave up
+          // first) there is no barrier phase to wait for; a TMA load lands within microseconds, so pause well beyond that.
           const unsigned long long t0 = globaltimer();
           while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
         }

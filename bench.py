@@ -233,7 +233,7 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     burst, sustained, kind = peaks()
     b2b = res["ctapp"][1]
     return {"workload": f"TP{t} layer boundary {args.shape}, M={M}, producer K={Kr} N=8192 -> reduce + residual + RMSNorm -> consumer N={N2r}",
-            "n_gpus": t, "fusion": args.fusion, "steal": steal, "R": bd.R, "red_blocks": bd.red_blocks, "red_threads": bd.red_threads, "producer_tile": "256x512" if bd.down_pair(M) == 2 else "256x256", "push": "nvls multimem" if bd.nvls else "unicast",
+            "n_gpus": t, "fusion": args.fusion, "steal": steal, "R": bd.R, "red_blocks": bd.red_blocks, "red_threads": bd.red_threads, "producer_tile": "256x512" if bd.down_pair(M) == 2 else "256x256", "push": ("nvls multimem + in-switch reduction" if bd.ldreduce else "nvls multimem") if bd.nvls else "unicast",
             "ms_median_b2b": {k: [round(v[0], 4), round(v[1], 4)] for k, v in res.items()},
             "speedup_vs_cublas_nccl_fusednorm_b2b": res["cublas_nccl_fusednorm"][1] / b2b,
             "over_two_gemm_floor_b2b": b2b / res["two_gemm_floor"][1],
@@ -425,7 +425,8 @@ def main():
     ap.add_argument("--red-threads", type=int, default=1024, help="boundary: threads per reducer CTA (<= 512 to share an SM with a GEMM CTA)")
     ap.add_argument("--no-sustained", action="store_true", help="chain: keep the one-second sustained loop as short as the timed region (profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="chain: skip the gated-latency, boundary and oracle records that follow the timed regions")
-    ap.add_argument("--protocol", default="v5", choices=["v5", "v3"], help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes")
+    ap.add_argument("--protocol", default="v5", choices=["v5", "v3", "v3r"],
+                    help="boundary: v5 = unicast pushes, v3 = NVLS multimem pushes, v3r = v3 + the cross-rank sum by multimem.ld_reduce inside the NVSwitch")
     ap.add_argument("--baselines", default="stock", choices=["stock", "strong"],
                     help="boundary: strong = also torch's multimem all-reduce and async-TP (fused matmul + reduce-scatter) boundaries")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")

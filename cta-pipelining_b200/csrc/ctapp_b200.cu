@@ -214,7 +214,8 @@ __global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb
 
 template <int W> static int launch_reduce(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
   constexpr int R = RedRows<W>::value;
-  if (p.x_mc) tp_reduce_kernel<W, R, true><<<blocks, threads, 0, s>>>(p);
+  if (p.partials_mc) tp_reduce_kernel<W, 4, true, true><<<blocks, threads, 0, s>>>(p);     // one reduced load per row: four rows in flight
+  else if (p.x_mc) tp_reduce_kernel<W, R, true><<<blocks, threads, 0, s>>>(p);
   else tp_reduce_kernel<W, R><<<blocks, threads, 0, s>>>(p);
   CU_OK(cudaGetLastError());
   return 0;
@@ -307,6 +308,11 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
     ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
     p.x_mc = static_cast<uint4*>(a->x_mc); p.rowss_mc = a->rowss_mc; p.panel_flag_mc = a->panel_flag_mc;
   }
+  if (a->partials_mc) {
+    ARG(p.x_mc, "the in-switch reduction (partials_mc) needs the NVLS pushes too (x_mc, rowss_mc, panel_flag_mc)");
+    ARG(!a->unit_ctr || !a->help_all, "the in-switch reduction is not available to helping consumer CTAs");
+    p.partials_mc = static_cast<const uint4*>(a->partials_mc);
+  }
   p.limit_ns = limit_ns();
   return 0;
 }
@@ -323,7 +329,7 @@ static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cud
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 3; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
+int ctapp_abi_version(void) { return 4; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;
@@ -391,6 +397,9 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, RedRows<2>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, RedRows<4>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, RedRows<8>::value, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 4, true, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 4, true, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 4, true, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false>));
@@ -504,7 +513,8 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
             a->panels_per_owner >= (a->M / 128 + a->world - 1) / a->world,
         "inbox slot of %d rows / %d panels per owner does not fit M=%d on %d ranks (panels_per_owner must be >= ceil(M/128/world) and its rows <= dst_rows)",
         a->dst_rows, a->panels_per_owner, a->M, a->world);
-    p.mode = kModeTpProducer;
+    ARG(!a->dst_global || a->dst_rows >= a->M, "dst_global: every destination must hold all M=%d rows (dst_rows %d)", a->M, a->dst_rows);
+    p.mode = kModeTpProducer; p.dst_global = a->dst_global != 0;
     p.world = a->world; p.rank = a->rank; p.ppo = a->panels_per_owner;
     for (int d = 0; d < a->world; d++) {
       ARG(a->dst_ptrs[d] && a->peer_tile_flags[d], "missing destination %d", d);
@@ -547,6 +557,7 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
     if (a->mode == 8) {
       if (int r = fill_reduce(a->red, p.red, true)) return r;
       ARG(p.red.unit_ctr, "mode 8 needs red->unit_ctr: the units are shared out through that counter");
+      ARG(!p.red.partials_mc, "mode 8: helping consumer CTAs read the inbox; the in-switch reduction (red->partials_mc) has no inbox");
       ARG(p.red.M == a->M && p.red.n1 == a->K, "mode 8: the reducer's shape (M=%d, n1=%d) must be this GEMM's (M=%d, K=%d)", p.red.M, p.red.n1, a->M, a->K);
     }
   } else {
@@ -576,7 +587,8 @@ int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* str
   ARG(a->M <= kNoAllocMaxM, "M=%d is beyond the built-in scratch of ctapp_tp_reduce_noalloc (at most %d rows); use ctapp_tp_reduce with caller buffers",
       a->M, kNoAllocMaxM);
   // what this variant does not do is refused, not dropped: a caller that set one of these would get other behaviour than it asked for
-  ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc, "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc must be NULL");
+  ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc && !a->partials_mc,
+      "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc / partials_mc must be NULL");
   ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger and help_all 0");
   ReduceParams p;
   if (int r = fill_reduce(a, p, false)) return r;

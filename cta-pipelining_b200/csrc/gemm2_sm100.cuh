@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
         ready_checked = true;
       }
       int dst = 0, drow = m * BM;
-      if (p.mode == kModeTpProducer) { dst = m % p.world; drow = (m / p.world) * BM; }
+      if (p.mode == kModeTpProducer) { dst = m % p.world; drow = p.dst_global ? m * BM : (m / p.world) * BM; }
       const CUtensorMap* tmD = &p.tmD[dst];
 
       const uint32_t tcol = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + a * BN;

@@ -62,6 +62,8 @@ struct alignas(64) GemmParams {
   int chunk_kblocks, chunk_cols, chunk_value;
   // tensor-parallel boundary
   int world, rank, ppo;
+  int dst_global;                    // producer: a tile's destination rows are its own rows (every tmD describes an (M, N) buffer, e.g.
+                                     // this rank's partial buffer for the in-switch reduction) instead of the owner's inbox rows
   int* peer_tile_flags[kMaxWorld];
   const int* epoch_ptr;
   int epoch;
@@ -378,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       }
       // destination of this tile
       int dst = 0, drow = m * BM;
-      if (p.mode == kModeTpProducer) { dst = m % p.world; drow = (m / p.world) * BM; }
+      if (p.mode == kModeTpProducer) { dst = m % p.world; drow = p.dst_global ? m * BM : (m / p.world) * BM; }
       const CUtensorMap* tmD = &p.tmD[dst];
 
       const uint32_t tcol = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + a * BN;

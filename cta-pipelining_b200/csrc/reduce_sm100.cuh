@@ -37,6 +37,9 @@ struct ReduceParams {
   uint4* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
+  // in-switch reduction: multicast address of the ranks' partial-sum buffers ((M, n1) bf16, every rank's own producer output at
+  // the same offset); null = the partials are read from the local inbox slices
+  const uint4* partials_mc;
 };
 
 // Unit u -> (owned panel j, n-tile, quarter).  The order follows the producer's tile order so that units become ready in
@@ -98,7 +101,9 @@ __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
 //     by ROWS lanes at once
 //   * lane 0 orders everything above before the panel's arrival count; the warp that completes the panel pushes the panel's
 //     128 row sums and then panel_flag[m] = epoch to every rank
-template <int W, int ROWS, bool MC>
+// LR (needs MC): the W partials are not read from the inbox but summed by the NVSwitch: one multimem.ld_reduce (fp32
+// accumulation in the switch, bf16 result) on the multicast address of the ranks' partial buffers replaces the W loads and adds.
+template <int W, int ROWS, bool MC, bool LR = false>
 __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, int u, int Pr, int tiles_n, int lane) {
   static_assert(ROWS == 1 || ROWS == 2 || ROWS == 4, "rows per batch");
   int j, n, q;
@@ -123,11 +128,16 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
   const bool rsrc = p.resid != nullptr;
 #pragma unroll 1
   for (int r = 0; r < 32; r += ROWS, ioff += static_cast<size_t>(ROWS) * row_vecs, xoff0 += static_cast<size_t>(ROWS) * row_vecs) {
-    uint4 part[ROWS][W], res[ROWS];
+    constexpr int kParts = LR ? 1 : W;
+    uint4 part[ROWS][kParts], res[ROWS];
 #pragma unroll
     for (int rr = 0; rr < ROWS; rr++) {
+      if (LR) {
+        part[rr][0] = multimem_ld_reduce_bf16x8(p.partials_mc + xoff0 + rr * row_vecs);   // the partials sit at x's own offsets
+      } else {
 #pragma unroll
-      for (int s = 0; s < W; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
+        for (int s = 0; s < kParts; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
+      }
     }
     if (rsrc) {
 #pragma unroll
@@ -141,7 +151,7 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
       for (int i = 0; i < 4; i++) {
         float lo = -0.0f, hi = -0.0f;
 #pragma unroll
-        for (int s = 0; s < W; s++) { const uint32_t w = (&part[rr][s].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
+        for (int s = 0; s < kParts; s++) { const uint32_t w = (&part[rr][s].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
         if (rsrc) { const uint32_t w = (&res[rr].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
         o[i] = pack_bf16x2(lo, hi);
       }
@@ -217,7 +227,7 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
 // next unit from the shared counter instead (first / stride unused), which lets CTAs of another kernel join in.
 // kOnlyReady (helpers from another kernel): a warp takes a unit only while the NEXT unclaimed unit's tile has already arrived,
 // i.e. while the dedicated reducer CTAs are behind the producers; once the reducers keep pace it leaves instead of waiting.
-template <int W, int ROWS, bool MC, bool kOnlyReady = false>
+template <int W, int ROWS, bool MC, bool kOnlyReady = false, bool LR = false>
 __device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, int first, int stride, int lane) {
   const int P = p.M / 128;
   const int Pr = P > p.rank ? (P - 1 - p.rank) / W + 1 : 0;
@@ -239,7 +249,7 @@ __device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, i
     return __shfl_sync(0xffffffffu, v, 0);
   };
   for (int u = p.unit_ctr ? claim() : first; u < U; u = p.unit_ctr ? claim() : u + stride)
-    if (!reduce_unit<W, ROWS, MC>(p, epoch, u, Pr, tiles_n, lane)) return;   // a producer never delivered: the host reads the status
+    if (!reduce_unit<W, ROWS, MC, LR>(p, epoch, u, Pr, tiles_n, lane)) return;   // a producer never delivered: the host reads the status
 }
 
 // rows per batch: as many as the register file of a 1024-thread CTA allows (64 registers per thread)
@@ -247,12 +257,12 @@ template <int W> struct RedRows { static constexpr int value = W >= 8 ? 1 : (W >
 
 // MC: the pushes to every rank (x rows, row sums, panel flags) are single multimem stores on a multicast address, replicated
 // by the NVSwitch, instead of one unicast store per rank; everything else is the same kernel.
-template <int W, int ROWS, bool MC = false>
+template <int W, int ROWS, bool MC = false, bool LR = false>
 __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p) {
   if (p.pdl_trigger) pdl_launch_dependents();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  reduce_units<W, ROWS, MC>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x) * nwarps, lane);
+  reduce_units<W, ROWS, MC, false, LR>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x) * nwarps, lane);
 }
 
 // Consumer CTAs helping the owner reducer (any CTA shape): every warp claims units while there are units whose tiles have

@@ -24,7 +24,7 @@ SOURCES = ["ctapp_b200.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-ABI_VERSION = 3
+ABI_VERSION = 4
 STATUS_INTS = 8
 MAX_WORLD = 8
 
@@ -92,7 +92,7 @@ class TpDownArgs(C.Structure):
                 ("epoch", C.c_int), ("epoch_dev", C.c_void_p), ("dst_ptrs", C.c_void_p * MAX_WORLD), ("dst_rows", C.c_int),
                 ("peer_tile_flags", C.c_void_p * MAX_WORLD), ("panels_per_owner", C.c_int), ("sms", C.c_int),
                 ("pdl_trigger", C.c_int), ("pdl", C.c_int), ("tail_cols", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p),
-                ("cta_pair", C.c_int), ("tile_log", C.c_void_p)]
+                ("cta_pair", C.c_int), ("dst_global", C.c_int), ("tile_log", C.c_void_p)]
 
 
 class TpQkvArgs(C.Structure):
@@ -109,7 +109,7 @@ class TpReduceArgs(C.Structure):
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("order", C.c_int), ("swz", C.c_int), ("unit_ctr", C.c_void_p),
                 ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("help_all", C.c_int), ("trace", C.c_void_p),
-                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p)]
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("partials_mc", C.c_void_p)]
 
 
 _SIGS = {
@@ -385,7 +385,7 @@ class Tp4Module:
     def tp4_down(self, A, W, D, raster, swizzle, mode, rank, world, epoch, tile_cnt_mc=0, tile_cnt=None, partials_mc=0, x_mc=0,
                  resid=None, rowss_mc=0, panel_cnt_mc=0, sms=0, epoch_dev=None, rowss_mc_base=0, rowss_stride=0, d_ptr=0,
                  dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None, cta_pair=0,
-                 tile_log=None):
+                 tile_log=None, dst_global=0):
         A, W = _bf16_matrix(A, "A"), _bf16_matrix(W, "W")
         if mode not in (0, 7):
             raise RuntimeError(f"tp4_down: mode {mode} is not available in this build (0 | 7)")
@@ -400,14 +400,14 @@ class Tp4Module:
         a.dst_ptrs, a.dst_rows = _ptr_array(dst_ptrs), int(dst_rows)
         a.peer_tile_flags, a.panels_per_owner = _ptr_array(peer_tile_flags), int(panels_per_owner)
         a.sms, a.pdl_trigger, a.pdl, a.tail_cols = int(sms), int(pdl_trigger), int(pdl), int(tail_cols)
-        a.trace, a.status, a.cta_pair, a.tile_log = _ptr(trace), _ptr(status), int(cta_pair), _ptr(tile_log)
+        a.trace, a.status, a.cta_pair, a.tile_log, a.dst_global = _ptr(trace), _ptr(status), int(cta_pair), _ptr(tile_log), int(dst_global)
         dev = A.device.index
         _check(self.lib.ctapp_tp_down(C.byref(a), dev, _stream(dev)))
 
     @staticmethod
     def _reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                      rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=1, swz=1, unit_ctr=0, unit_log=None, pdl_trigger=0,
-                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0):
+                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0, partials_mc_ptr=0):
         """The owner reducer's argument block (``ctapp_tp_reduce_args``), shared by tp4_reduce, tp4_reduce_noalloc and the mode-8
         consumer.  ``panels_per_owner`` is required: the flags are indexed with it, and a wrong value aliases the sources."""
         if panels_per_owner <= 0:
@@ -424,6 +424,7 @@ class Tp4Module:
         a.unit_ctr, a.unit_log, a.pdl_trigger, a.help_all = _ptr(unit_ctr), _ptr(unit_log), int(pdl_trigger), int(help_all)
         a.trace, a.status = _ptr(red_trace), _ptr(status)
         a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
+        a.partials_mc = _ptr(partials_mc_ptr)
         return a
 
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
@@ -465,7 +466,8 @@ class Tp4Module:
     def tp4_reduce(self, M, rank, world, epoch, raster, blocks, tile_cnt, partials_mc=0, x_mc=0, resid=None, rowss_mc=0, panel_cnt_mc=0,
                    unicast=0, peer_partials=(), peer_x=(), version=5, epoch_dev=None, inbox_ptrs=(), peer_rowss=(), peer_panel_flag=(),
                    rowss_local=0, panel_done=0, panels_per_owner=0, threads=1024, variant=1, swz=1, rows=2, red_trace=0, dsmem=0, stages=0,
-                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, unit_log=None):
+                   unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, unit_log=None,
+                   partials_mc_ptr=0):
         """Owner reducer, protocol version 5 (``raster`` = the producer's tile order: 1 = m fastest, 2 = n fastest; ``swz`` = its
         n-tile group size).  ``variant`` / ``rows`` / ``stages`` / ``dsmem`` of the reference select kernels that have one
         counterpart here and are accepted without effect."""
@@ -474,7 +476,7 @@ class Tp4Module:
         a = self._reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_cnt, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                               rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=2 if raster == 2 else 1, swz=swz,
                               unit_ctr=unit_ctr, unit_log=unit_log, pdl_trigger=pdl_trigger, red_trace=red_trace, x_mc_ptr=x_mc_ptr,
-                              rowss_mc_ptr=rowss_mc_ptr, panel_flag_mc_ptr=panel_flag_mc_ptr)
+                              rowss_mc_ptr=rowss_mc_ptr, panel_flag_mc_ptr=panel_flag_mc_ptr, partials_mc_ptr=partials_mc_ptr)
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
 

@@ -94,14 +94,15 @@ class _Buffers:
     """Everything a boundary instance keeps on its GPU: the symmetric buffers of ``_SYMMETRIC`` (tensor + handle each), the
     per-rank scratch, and the address tables the kernels take, derived from the handles."""
 
-    def __init__(self, sizes, dev, group, rank, want_multicast):
+    def __init__(self, sizes, dev, group, rank, want_multicast, with_partials=False):
         self.z, self.dev, self.rank = sizes, dev, rank
         self.handles = {}
-        for name, shape, dtype, mc in _SYMMETRIC:
+        table = _SYMMETRIC + ((("partials", lambda z: (z.max_M, z.n1), DTYPE, True),) if with_partials else ())   # in-switch reduction
+        for name, shape, dtype, mc in table:
             t, h = _symm(shape(sizes), dtype, dev, group, rank, mc and want_multicast)
             setattr(self, name, t)
             self.handles[name] = h
-        self.multicast = want_multicast and all(self.handles[n].multicast_ptr for n, _, _, mc in _SYMMETRIC if mc)
+        self.multicast = want_multicast and all(self.handles[n].multicast_ptr for n, _, _, mc in table if mc)
         z = sizes
         self.rowss_local = torch.zeros(z.max_M, dtype=torch.float32, device=dev)      # owner's accumulators, zeroed per step
         self.panel_done = torch.zeros(z.P, dtype=torch.int32, device=dev)             # arrivals per owned panel
@@ -129,7 +130,9 @@ class _Buffers:
             peer_pf=self.peers("panel_flag"),
             x_mc=[self.mc("xbuf"), self.mc("xbuf1")],
             rowss_mc=[self.mc("rowss", par * z.max_M * 4) for par in (0, 1)],
-            pf_mc=self.mc("panel_flag"))
+            pf_mc=self.mc("panel_flag"),
+            partials_local=self.partials.data_ptr() if "partials" in self.handles else 0,
+            partials_mc=self.mc("partials") if "partials" in self.handles else 0)
 
 
 class _GraphCache:
@@ -155,9 +158,11 @@ class _GraphCache:
 
 
 def _check_options(world, protocol, fusion, steal, qkv_tile, down_tail, n1, act, cta_pair, N2r, M, max_M):
+    if protocol == "v3r" and steal:
+        raise ValueError("protocol 'v3r' (in-switch reduction) has no inbox for the consumer's CTAs to read: steal is not available with it")
     if world not in (1, 2, 4, 8):
         raise ValueError(f"world {world} is not supported (1 | 2 | 4 | 8)")
-    if protocol not in (True, False, "v3", "v5"):
+    if protocol not in (True, False, "v3", "v3r", "v5"):
         raise ValueError(f"unknown protocol {protocol!r}")
     if fusion == "role":
         raise ValueError("fusion='role' (the first R consumer CTAs ARE the reducer) is not built; steal=True gives every consumer CTA the "
@@ -186,7 +191,11 @@ class CtappBoundary:
     protocol: "v5" (default here) = unicast pushes; True / "v3" = NVLS variant: the same panel-ownership protocol, but the owner
     reducer pushes x, the row sums and the panel flags with ``multimem.st`` on multicast addresses, so each row leaves the
     owner once and the NVSwitch replicates it (needs one process per GPU, >= 2 ranks, torch symmetric memory with multicast;
-    falls back to unicast with a warning otherwise).  False = the two GEMMs alone (no exchange, no residual): the floor the
+    falls back to unicast with a warning otherwise).  "v3r" = "v3" plus the in-switch reduction of the reference's v3 reducer
+    (csrc/ctapp_tp4.cuh:458-536): every producer keeps its partial tiles in its own memory and only raises the owner's tile
+    flag; the owner reads each 16 bytes of the cross-rank sum with one ``multimem.ld_reduce`` (fp32 accumulation inside the
+    switch) instead of ``world`` loads from its inbox.  Same flags and order as v5; the values agree with v5 within the
+    boundary's tolerance, not bit for bit (the switch does not round to nearest even, and the residual is added afterwards).  False = the two GEMMs alone (no exchange, no residual): the floor the
     protocol is measured against.
     fusion: "none" = reducer on a side stream, consumer after the producer in stream order;
             "pdl"  = as "none" and the consumer is launched as the producer's programmatic dependent, so its CTAs start
@@ -244,16 +253,17 @@ class CtappBoundary:
         self.down_raster, self.down_swizzle, self.down_tail = down_raster or 1, down_swizzle, down_tail
         self.pdl_trigger = int(fusion in ("pdl", "pdl1")) if pdl_trigger is None else int(pdl_trigger)
         self.trace = bool(int(os.environ.get("CTAPP_TRACE", "0"))) if trace is None else bool(trace)
-        want_mc = protocol in (True, "v3") and world >= 2 and not isinstance(group_name, LocalGroup)
-        if protocol in (True, "v3") and not want_mc:
+        want_mc = protocol in (True, "v3", "v3r") and world >= 2 and not isinstance(group_name, LocalGroup)
+        if protocol in (True, "v3", "v3r") and not want_mc:
             log.warning("ctapp: NVLS needs one process per GPU and at least 2 ranks; using unicast pushes")
         sizes = _Sizes(max_M, n1, world)
         with torch.cuda.device(self.dev):
             self.ext.preload(self.dev.index)
-            self.buf = _Buffers(sizes, self.dev, group_name, rank, want_mc)
+            self.buf = _Buffers(sizes, self.dev, group_name, rank, want_mc, with_partials=want_mc and protocol == "v3r")
             if want_mc and not self.buf.multicast:
                 log.warning("ctapp: no multicast address on this system; using unicast pushes")
             self.nvls = self.buf.multicast
+            self.ldreduce = self.nvls and protocol == "v3r"       # the switch sums the partials; producers store locally
             self.tab = self.buf.tables()
             self.trace_down = torch.zeros(self.nsm * 8, dtype=torch.int64, device=self.dev)
             self.trace_qkv = torch.zeros(self.nsm * 8, dtype=torch.int64, device=self.dev)
@@ -325,12 +335,17 @@ class CtappBoundary:
         self.ext.tp4_reduce(M, self.rank, self.world, 0, self.down_raster, self.red_blocks, self.buf.tile_flags, version=5,
                             epoch_dev=self.buf.epoch_dev, threads=self.red_threads, swz=self.down_swizzle, n1=self.n1,
                             unit_ctr=self.buf.role_ctr[1:] if self.steal else 0, tail_cols=self.tail_cols(M),
-                            pdl_trigger=int(self.fusion == "pdl1"), unit_log=unit_log, **self._reducer_kwargs(M, resid, parity))
+                            pdl_trigger=int(self.fusion == "pdl1"), unit_log=unit_log,
+                            partials_mc_ptr=self.tab["partials_mc"] if self.ldreduce else 0, **self._reducer_kwargs(M, resid, parity))
 
     def launch_producer(self, h_r, Wd, M, tile_log=None, sms=None):
         t = self.tab
+        if self.ldreduce:      # every "destination" is this rank's own partial buffer, rows in place: only the flags travel
+            dst = dict(dst_ptrs=[t["partials_local"]] * self.world, dst_rows=self.max_M, dst_global=1)
+        else:
+            dst = dict(dst_ptrs=t["dst_ptrs"], dst_rows=self.ppo * 128)
         self.ext.tp4_down(h_r, Wd, None, self.down_raster, self.down_swizzle, 7, self.rank, self.world, 0, sms=self.sms if sms is None else sms,
-                          epoch_dev=self.buf.epoch_dev, dst_ptrs=t["dst_ptrs"], dst_rows=self.ppo * 128, peer_tile_flags=t["peer_tf"],
+                          epoch_dev=self.buf.epoch_dev, peer_tile_flags=t["peer_tf"], **dst,
                           panels_per_owner=self.ppo, pdl_trigger=self.pdl_trigger, pdl=int(self.fusion == "pdl1"),
                           trace=self._stamps(self.trace_down), tail_cols=self.tail_cols(M), status=self.buf.status, cta_pair=self.down_pair(M),
                           tile_log=tile_log)
@@ -523,7 +538,7 @@ class CtappBoundaryPool:
 
     def __init__(self, Kr, N2r, rank, world, group_name, device, R=None, min_M=512, max_instances=4,
                  qkv_raster=2, qkv_swizzle=1, protocol="v5", max_M=8192, **v5kw):
-        assert protocol in ("v3", "v5"), protocol
+        assert protocol in ("v3", "v3r", "v5"), protocol
         self.Kr, self.N2r, self.rank, self.world, self.gn, self.dev = Kr, N2r, rank, world, group_name, device
         self.R, self.min_M, self.max_instances = R, min_M, max_instances
         self.qkv_raster, self.qkv_swizzle = qkv_raster, qkv_swizzle

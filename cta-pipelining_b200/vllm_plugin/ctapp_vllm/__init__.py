@@ -18,8 +18,8 @@ def knobs(env=None):
     fusion = e.get("CTAPP_FUSION", "pdl")
     if mode not in ("both", "down", "oproj"):
         raise ValueError(f"CTAPP_BOUNDARY={mode!r}: expected both | down | oproj")
-    if proto not in ("v3", "v5"):
-        raise ValueError(f"CTAPP_PROTO={proto!r}: expected v3 | v5")
+    if proto not in ("v3", "v3r", "v5"):
+        raise ValueError(f"CTAPP_PROTO={proto!r}: expected v3 | v3r | v5")
     if fusion not in ("none", "pdl", "pdl1"):
         raise ValueError(f"CTAPP_FUSION={fusion!r}: this build has none | pdl | pdl1 (role: use CTAPP_STEAL=1)")
     tile = int(e.get("CTAPP_QKV_TILE", "256"))

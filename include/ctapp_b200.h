@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 3 */
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 4 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);
@@ -140,6 +140,12 @@ typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0
   int cta_pair;                            /* 0 = one CTA per 128-row tile; 1 = two CTAs per 256-row tile (cta_group::2), 256
                                               columns wide; 2 = the same on 256 x 512 tiles (N % 512 == 0; a tile raises the two
                                               256-column tile flags it covers; a quarter less operand traffic per FLOP) */
+  int dst_global;                          /* mode 7: 1 = a tile keeps its own row position in every destination (each dst_ptrs[d]
+                                              is then an (M, N) buffer, dst_rows >= M) instead of moving to row block m / world of
+                                              the owner's inbox slot.  With every dst_ptrs[d] = this rank's partial buffer the
+                                              producer stores locally and only the tile flag crosses the link: the layout the
+                                              in-switch reduction reads (ctapp_tp_reduce_args.partials_mc; the reference's producer
+                                              mode 4, csrc/ctapp_tp4.cuh:284-289) */
   int* tile_log;                           /* NULL, or [0] = 0 on entry and room for 1 + #tiles ints: the kernel appends one packed
                                               (m << 16 | n) per tile in the order its schedulers take them (m = tile row of the
                                               schedule: 256 rows with cta_pair); with one CTA (pair) that is the tile order itself */
@@ -206,6 +212,12 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   void* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
+  /* In-switch reduction (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.ld_reduce): multicast address of the ranks' partial
+   * buffers, (M, n1) bf16 each, written by producers launched with dst_global.  The W loads and adds per output become one
+   * multimem.ld_reduce.add.acc::f32.v4.bf16x2; `inbox` is not read.  The switch's bf16 result is not always the nearest
+   * bf16 of the fp32 sum, and the residual is added after that rounding: results agree with the inbox path within the
+   * boundary's tolerance, not bit for bit.  Needs the NVLS pushes above; NULL = read the inbox. */
+  const void* partials_mc;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 

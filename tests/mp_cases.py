@@ -88,8 +88,11 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     Kr, N2r = K // world, N2_ // world
     max_M = max(Ms)
     bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, steal=steal)
-    if protocol == "v3" and not bd.nvls:
+    if protocol in ("v3", "v3r") and not bd.nvls:
         return ["SKIP: no multicast address on this system"]
+    # in-switch reduction: the switch's bf16 result is not always the nearest one and the residual is added after it, so x may
+    # sit two bf16 steps from the model; the RMS-normalised bounds are the same
+    x_ulp, out_ulp, steps = (0.99, 0.98, 1) if protocol != "v3r" else (0.97, 0.90, 2)
     for it, M in enumerate(Ms):
         Wd, gamma, Wq = ob.make_weights(seed=1 + it, K=K, N2_=N2_, n1=n1)
         wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, rank, world)
@@ -98,13 +101,14 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
         bd.check()
         x_model, out_model = ob.boundary_device_model(h, Wd, resid, gamma, Wq, world)
         x = bd.x().cpu()
-        ulp = lambda a, b: ((a.view(torch.int16).int() - b.view(torch.int16).int()).abs() <= 1).float().mean().item()  # noqa: E731
-        if ulp(x, x_model) < 0.99:
-            fails.append(f"M={M}: x within one ulp only {ulp(x, x_model):.4f}")
+        ulp = lambda a, b: ((a.view(torch.int16).int() - b.view(torch.int16).int()).abs() <= steps).float().mean().item()  # noqa: E731
+        mxx, meanx = oc.error_stats(x, x_model)
+        if ulp(x, x_model) < x_ulp or not (mxx <= 2e-2 and meanx <= 1e-3):
+            fails.append(f"M={M}: x within {steps} ulp only {ulp(x, x_model):.4f}, max {mxx:.3e} mean {meanx:.3e}")
         o = out.cpu()
         om = out_model[:, rank * N2r:(rank + 1) * N2r]
         mx, mean = oc.error_stats(o, om)
-        if not (mx <= 2e-2 and mean <= 1e-3 and ulp(o, om) >= 0.98):
+        if not (mx <= 2e-2 and mean <= 1e-3 and ulp(o, om) >= out_ulp):
             fails.append(f"M={M}: out max {mx:.3e} mean {mean:.3e} ulp {ulp(o, om):.4f}")
         bits = [None] * world
         dist.all_gather_object(bits, int(x.view(torch.int16).to(torch.int64).sum().item()), group=tp4.GLOO)

@@ -31,7 +31,7 @@ def test_argument_errors_without_gpu():
     """Calls that fail in argument checking never touch CUDA, so they can run here."""
     from ctapp import ext
     lib = ext.lib()
-    assert lib.ctapp_abi_version() == ext.ABI_VERSION == 3
+    assert lib.ctapp_abi_version() == ext.ABI_VERSION == 4
     buf = ctypes.create_string_buffer(256)
     assert lib.ctapp_config_info(3, buf, 256) == 0 and b"tile 128x256x64" in buf.value
     assert lib.ctapp_config_info(5, buf, 256) == 0 and b"tile 128x128x64" in buf.value
@@ -66,7 +66,7 @@ def test_reducer_argument_checks_without_gpu():
     with pytest.raises(RuntimeError):
         _reduce_args(panels_per_owner=0)                       # the binding insists on the argument
     for over, word in ((dict(x_mc_ptr=0x2000, rowss_mc_ptr=0x2000, panel_flag_mc_ptr=0x2000), b"unicast"), (dict(unit_ctr=0x2000), b"unit_ctr"),
-                       (dict(unit_log=0x2000), b"unit_ctr"), (dict(pdl_trigger=1), b"pdl_trigger"), (dict(M=32768, panels_per_owner=128), b"16384")):
+                       (dict(unit_log=0x2000), b"unit_ctr"), (dict(pdl_trigger=1), b"pdl_trigger"), (dict(partials_mc_ptr=0x2000), b"unicast"), (dict(M=32768, panels_per_owner=128), b"16384")):
         a = _reduce_args(**over)
         assert lib.ctapp_tp_reduce_noalloc(ctypes.byref(a), 0, None) == -1, over
         assert word in lib.ctapp_last_error(), (over, lib.ctapp_last_error())

@@ -26,8 +26,9 @@ def test_nvls_probes():
     _run(mp_cases.nvls_probes, 29711)
 
 
-@pytest.mark.parametrize("protocol,fusion,cta_pair,steal", [("v5", "pdl", True, 1), ("v3", "pdl1", True, 1), ("v3", "none", False, 0), ("v3", "pdl", True, 0)])
+@pytest.mark.parametrize("protocol,fusion,cta_pair,steal", [("v5", "pdl", True, 1), ("v3", "pdl1", True, 1), ("v3", "none", False, 0), ("v3", "pdl", True, 0),
+                                                                  ("v3r", "pdl", True, 0), ("v3r", "none", False, 0)])
 def test_boundary_one_process_per_gpu(protocol, fusion, cta_pair, steal):
     import mp_cases
-    port = 29712 + ["v5", "v3"].index(protocol) * 4 + int(cta_pair) * 2 + steal
+    port = 29712 + ["v5", "v3", "v3r"].index(protocol) * 4 + int(cta_pair) * 2 + steal
     _run(mp_cases.boundary_case, port, protocol, fusion, cta_pair, (1024, 256, 768, 1024), 2048, 8192, 2048, bool(steal))

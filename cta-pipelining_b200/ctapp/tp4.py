@@ -533,117 +533,133 @@ class CtappBoundaryPool:
     ``get(M)`` returns None when M is unsupported (M % 128 != 0, M < min_M or M > max_M): the caller uses its stock
     path.  Otherwise it returns the single instance sized ``max_M`` (value flags make it serve every M), creating it
     on first use.  Creation is COLLECTIVE (symmetric allocation + barrier): every rank must make its first valid
-    ``get`` at the same point.  Same constructor as reference ctapp/tp4.py:507-554; ``protocol`` "v3" and "v5" both map
-    to the unicast panel-ownership protocol here.
+    ``get`` at the same point.  Same constructor as reference ctapp/tp4.py:507-554; ``max_instances`` is accepted for that
+    reason (one instance serves every M here whatever the protocol).
     """
 
     def __init__(self, Kr, N2r, rank, world, group_name, device, R=None, min_M=512, max_instances=4,
                  qkv_raster=2, qkv_swizzle=1, protocol="v5", max_M=8192, **v5kw):
-        assert protocol in ("v3", "v3r", "v5"), protocol
-        self.Kr, self.N2r, self.rank, self.world, self.gn, self.dev = Kr, N2r, rank, world, group_name, device
-        self.R, self.min_M, self.max_instances = R, min_M, max_instances
-        self.qkv_raster, self.qkv_swizzle = qkv_raster, qkv_swizzle
-        self.protocol, self.max_M = protocol, max_M
-        self.v5kw = v5kw
-        self._inst = {}
+        if protocol not in ("v3", "v3r", "v5"):
+            raise ValueError(f"unknown protocol {protocol!r}")
+        self.min_M, self.max_M, self.max_instances, self.protocol = min_M, max_M, max_instances, protocol
+        self._where = (Kr, N2r, rank, world, group_name, device)
+        self._options = dict(R=R, qkv_raster=qkv_raster, qkv_swizzle=qkv_swizzle, protocol=protocol, max_M=max_M, **v5kw)
+        self._inst = {}       # max_M -> instance (at most one entry)
+
+    def supports(self, M):
+        return M % 128 == 0 and self.min_M <= M <= self.max_M
 
     def get(self, M):
-        if M % 128 != 0 or M < self.min_M or M > self.max_M:
+        if not self.supports(M):
             return None
-        bd = self._inst.get(self.max_M)
-        if bd is None:
-            bd = CtappBoundary(self.max_M, self.Kr, self.N2r, self.rank, self.world, self.gn, self.dev, R=self.R,
-                               qkv_raster=self.qkv_raster, qkv_swizzle=self.qkv_swizzle, protocol=self.protocol, max_M=self.max_M, **self.v5kw)
-            self._inst[self.max_M] = bd
-        return bd
+        if self.max_M not in self._inst:
+            self._inst[self.max_M] = CtappBoundary(self.max_M, *self._where, **self._options)
+        return self._inst[self.max_M]
 
 
-# --------------------------------------------------------------------------- baselines
-class _Base:
+# --------------------------------------------------------------------------- comparison boundaries
+class _StockBoundary:
+    """What the pipelined boundary is compared with: down-projection, some all-reduce, add + RMSNorm, next projection, each a
+    separate step.  Subclasses say how the partial sums are reduced (``reduced``) and how the norm is applied (``normed``);
+    ``forward(h_r, resid)`` and ``x()`` are the pipelined boundary's."""
+
     def __init__(self, M, rank, world, group_name, device, Wdown_r, Wqkv_r, gamma):
         self.M, self.rank, self.world, self.gn, self.dev = M, rank, world, group_name, device
-        self.Wd, self.Wq, self.gamma = Wdown_r, Wqkv_r, gamma.to(DTYPE)
-        self._x = None
+        self.w_down, self.w_next, self.gamma = Wdown_r, Wqkv_r, gamma.to(DTYPE)
+        self.residual = None
 
     def x(self):
-        return self._x
+        return self.residual
 
-    def _post(self, y, resid):
-        x = y + resid if resid is not None else y
-        self._x = x
-        return torch.mm(rmsnorm_gamma(x, self.gamma), self.Wq.t())
+    def partial(self, h_r):
+        return torch.mm(h_r, self.w_down.t())
 
+    def reduced(self, y):
+        return y
 
-class NcclBoundary(_Base):
-    """cuBLAS GEMM + NCCL all-reduce + eager add and RMSNorm + cuBLAS GEMM (reference ctapp/tp4.py:641-645)."""
+    def normed(self, y, resid):
+        """(new residual, normalised activations)"""
+        x = y if resid is None else y + resid
+        return x, rmsnorm_gamma(x, self.gamma)
 
     def forward(self, h_r, resid=None):
-        y = torch.mm(h_r, self.Wd.t())
+        self.residual, n = self.normed(self.reduced(self.partial(h_r)), resid)
+        return torch.mm(n, self.w_next.t())
+
+
+class NcclBoundary(_StockBoundary):
+    """cuBLAS GEMM + NCCL all-reduce + eager add and RMSNorm + cuBLAS GEMM (reference ctapp/tp4.py:641-645)."""
+
+    def reduced(self, y):
         if self.world > 1:
             dist.all_reduce(y)
-        return self._post(y, resid)
+        return y
 
 
-class NcclFusedNormBoundary(_Base):
+class NcclFusedNormBoundary(NcclBoundary):
     """The stock serving-stack boundary: cuBLAS GEMM + NCCL all-reduce + ONE fused add+RMSNorm kernel + cuBLAS GEMM.
     This is the baseline the pipelined boundary has to beat (the reference's own caveat: its NCCL row carried an
-    unfused norm, results/tp4_chain.md:3-11)."""
+    unfused norm, results/tp4_chain.md:3-11).  Works in preallocated buffers."""
 
     def __init__(self, *a):
         super().__init__(*a)
         self.ext = load_tp4()
-        n1 = self.Wd.shape[0]
-        self.y = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.xn = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.xo = torch.empty(self.M, n1, dtype=DTYPE, device=self.dev)
-        self.out = torch.empty(self.M, self.Wq.shape[0], dtype=DTYPE, device=self.dev)
+        n1 = self.w_down.shape[0]
+        new = lambda cols: torch.empty(self.M, cols, dtype=DTYPE, device=self.dev)  # noqa: E731
+        self.y, self.xn, self.xo, self.out = new(n1), new(n1), new(n1), new(self.w_next.shape[0])
+
+    def partial(self, h_r):
+        return torch.mm(h_r, self.w_down.t(), out=self.y[:h_r.shape[0]])
+
+    def normed(self, y, resid):
+        rows = y.shape[0]
+        self.ext.add_rmsnorm(y, resid, self.gamma, self.xo[:rows], self.xn[:rows])
+        return self.xo[:rows], self.xn[:rows]
 
     def forward(self, h_r, resid=None):
-        M = h_r.shape[0]
-        torch.mm(h_r, self.Wd.t(), out=self.y[:M])
-        if self.world > 1:
-            dist.all_reduce(self.y[:M])
-        self.ext.add_rmsnorm(self.y[:M], resid, self.gamma, self.xo[:M], self.xn[:M])
-        self._x = self.xo[:M]
-        return torch.mm(self.xn[:M], self.Wq.t(), out=self.out[:M])
+        self.residual, n = self.normed(self.reduced(self.partial(h_r)), resid)
+        return torch.mm(n, self.w_next.t(), out=self.out[:n.shape[0]])
 
 
-class MultimemBoundary(_Base):
+class MultimemBoundary(_StockBoundary):
     """cuBLAS GEMM into a symmetric buffer + torch's in-switch (multimem) all-reduce + eager add and norm (reference
     ctapp/tp4.py:573-583).  Needs torch symmetric memory with multicast support."""
 
     def __init__(self, *a):
         super().__init__(*a)
-        import torch.distributed._symmetric_memory as symm_mem
-        self.y = symm_mem.empty(self.M, self.Wd.shape[0], dtype=DTYPE, device=self.dev)
-        self._h = symm_mem.rendezvous(self.y, self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name)
+        import torch.distributed._symmetric_memory as sm
+        self._group = self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name
+        self.y = sm.empty(self.M, self.w_down.shape[0], dtype=DTYPE, device=self.dev)
+        self._handle = sm.rendezvous(self.y, self._group)
 
-    def forward(self, h_r, resid=None):
-        torch.mm(h_r, self.Wd.t(), out=self.y)
-        torch.ops.symm_mem.multimem_all_reduce_(self.y, "sum", self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name)
-        return self._post(self.y, resid)
+    def partial(self, h_r):
+        return torch.mm(h_r, self.w_down.t(), out=self.y)
+
+    def reduced(self, y):
+        torch.ops.symm_mem.multimem_all_reduce_(y, "sum", self._group)
+        return y
 
 
-class AsyncTpBoundary(_Base):
+class AsyncTpBoundary(_StockBoundary):
     """torch's fused matmul + reduce-scatter (the async-TP decomposition), norm on the own rows, all-gather, GEMM (reference
     ctapp/tp4.py:621-638)."""
 
     def __init__(self, *a):
         super().__init__(*a)
-        import torch.distributed._symmetric_memory as symm_mem
-        self._gname = self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name
-        symm_mem.enable_symm_mem_for_group(self._gname)
-        self.full = torch.empty(self.M, self.Wd.shape[0], dtype=DTYPE, device=self.dev)
+        import torch.distributed._symmetric_memory as sm
+        self._group = self.gn if isinstance(self.gn, str) else dist.group.WORLD.group_name
+        sm.enable_symm_mem_for_group(self._group)
+        self.gathered = torch.empty(self.M, self.w_down.shape[0], dtype=DTYPE, device=self.dev)
 
     def forward(self, h_r, resid=None):
-        from torch.distributed._symmetric_memory import _fused_matmul_reduce_scatter
-        m = self.M // self.world
-        ys = _fused_matmul_reduce_scatter(h_r, self.Wd.t(), "sum", 0, self._gname)
+        from torch.distributed._symmetric_memory import _fused_matmul_reduce_scatter as matmul_rs
+        rows = self.M // self.world
+        mine = matmul_rs(h_r, self.w_down.t(), "sum", 0, self._group)
         if resid is not None:
-            ys = ys + resid[self.rank * m:(self.rank + 1) * m]
-        self._x = ys                                             # own rows only
-        dist.all_gather_into_tensor(self.full, rmsnorm_gamma(ys, self.gamma))
-        return torch.mm(self.full, self.Wq.t())
+            mine = mine + resid[self.rank * rows:(self.rank + 1) * rows]
+        self.residual = mine                                      # own rows only
+        dist.all_gather_into_tensor(self.gathered, rmsnorm_gamma(mine, self.gamma))
+        return torch.mm(self.gathered, self.w_next.t())
 
 
 # --------------------------------------------------------------------------- references

@@ -103,7 +103,7 @@ class CtappLlamaModel(LlamaModel):
             if not wanted:
                 out.append(None)
                 continue
-            creating = not pool._inst and M % 128 == 0 and k["min_M"] <= M <= k["max_M"]
+            creating = not pool._inst and pool.supports(M)
             if creating:
                 torch.cuda.synchronize()
                 get_tp_group().barrier()

@@ -145,7 +145,7 @@ def run_reference(args, rank):
 
 def workload_config(args, n):
     if args.cfg == "auto":
-        args.cfg = GEMM_CFG_WIDE if n <= 2 else GEMM_CFG
+        args.cfg = GEMM_CFG_WIDE
     args.cfg = int(args.cfg)
     return {"workload": f"{n}-stage layer-per-GPU bf16 linear chain, M={args.m} tokens, N=K={NK}, no activation, one stage per GPU"
                         + (" (N=1: one GEMM through the work-queue protocol)" if n == 1 else ""),
@@ -410,14 +410,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cfg", default="auto", choices=["auto", "3", "10", "11"],
                     help="chain: GEMM configuration id (10 = CTA pair on 256x256x64 tiles, 11 = CTA pair on 256x512x64, 3 = one CTA on "
-                    "128x256x64; auto = 11 on one and two GPUs, where it measured 5.5 %% and 2-6 %% faster, and 10 from three on, where the wider tile has not been timed)")
+                    "128x256x64; auto = 11: it measured 5.5 %% faster on one GPU, 2-6 %% on two and 3 %% in the one-second loop on four)")
     ap.add_argument("--tokens", dest="m", type=int, default=None, help="M, the number of token rows (default 8192 for the chain, 4096 for the boundary)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
-                    "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8 up to two GPUs, 'head' from "
-                    "three: steps overlap, so the fill is paid once per run and per link; on 2 GPUs 'head' measured 0.7-0.9 %% slower than 8)")
+                    "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8: 'head' "
+                    "measured 0.7-0.9 %% slower on 2 GPUs and 0.2-1 %% slower on 4)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
     ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = on at TP8 only: it measured neutral to slightly slower at TP2 and TP4")
     ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")
@@ -490,9 +490,11 @@ def main():
     X_dev = X_host.to(dev) if rank == 0 else None
     Y_host = torch.empty(M, NK, dtype=torch.bfloat16).pin_memory() if rank == n - 1 else None
 
-    args.cfg = (GEMM_CFG_WIDE if world <= 2 else GEMM_CFG) if args.cfg == "auto" else int(args.cfg)
+    # measured at N = 4 (20-step / one-second figures, ms per step): 256x512 tiles in groups of 8: 0.811 / 0.880; 256x256 in groups
+    # of 8: 0.810 / 0.906; 256x512 head-ramped: 0.813 / 0.891; 256x256 head-ramped: 0.829 / 0.927
+    args.cfg = GEMM_CFG_WIDE if args.cfg == "auto" else int(args.cfg)
     gr = args.group_rows
-    gr = (8 if world <= 2 else "head") if gr == "auto" else (gr if gr in ("ramp", "head") else int(gr))
+    gr = 8 if gr == "auto" else (gr if gr in ("ramp", "head") else int(gr))
     args.group_rows = gr
     if world == 1:
         chain = Chain(M, NK, [NK], [local_rank], cfg=args.cfg, group_rows=args.group_rows)

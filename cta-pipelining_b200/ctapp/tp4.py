@@ -217,8 +217,8 @@ class CtappBoundary:
     act: the consumer's weight is a gate/up projection with rows interleaved by ``interleave_gate_up``; its epilogue applies
     silu(gate) * up and ``out`` is (M, N2r / 2): the activation costs no pass over memory of its own.
     cta_pair: both GEMMs run as CTA pairs (``cta_group::2``, 256-row tiles; the protocol's unit stays the 128-row panel);
-    the producer then works on 256 x 512 tiles (raising two tile flags per tile) when M is large enough to give every pair
-    such a tile, on 256 x 256 tiles otherwise; "wide" / "narrow" force either; False = one CTA per 128-row tile.
+    the producer then works on 256 x 512 tiles (raising two tile flags per tile) up to TP2 when M is large enough to give
+    every pair such a tile, on 256 x 256 tiles otherwise; "wide" / "narrow" force either; False = one CTA per 128-row tile.
     ``group_name``: a torch.distributed group name (one process per GPU) or a ``ctapp.symm.LocalGroup`` (one process
     drives every rank's GPU).
     """
@@ -321,8 +321,8 @@ class CtappBoundary:
         if not self.cta_pair or self.n1 % 512:
             return self.cta_pair
         wide = self._down_wide
-        if wide is None:
-            wide = (M // 256) * (self.n1 // 512) >= self.sms // 2
+        if wide is None:      # measured at M=4096: TP2 (K=14336 per rank) gains 1.5-2 % on the whole boundary, TP4 (K=7168) loses 2 %:
+            wide = self.world <= 2 and (M // 256) * (self.n1 // 512) >= self.sms // 2      # coarser tiles reach the reducer later
         return 2 if wide else 1
 
     def _stamps(self, t):

@@ -198,7 +198,7 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     steal = bool(args.steal) if args.steal in (0, 1) else t >= 8
     bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion,
                            R=None if args.R < 0 else args.R, steal=steal, red_blocks=args.red_blocks if args.red_blocks >= 0 else None,
-                           red_threads=args.red_threads, red_variant=args.red_variant, cta_pair={1: "wide", 0: "narrow"}.get(args.down_wide, True), **akw)
+                           red_threads=args.red_threads, cta_pair={1: "wide", 0: "narrow"}.get(args.down_wide, True), **akw)
     bd.set_weights(Wd_r, Wqf_r)
     res["ctapp"] = tp4.time_step(lambda: bd.forward(h_r, resid), dev, iters, warm)
     bd.check()
@@ -302,7 +302,7 @@ def run_reducer(args, rank, world, local_rank):
     rv = {}
     resid = torch.randn(M, tp4.N1, device=dev).to(torch.bfloat16)
     for R in ([args.R] if args.R > 0 else [4, 8, 16, 32]):
-        bd = tp4.CtappBoundary(M, 256, 256, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, R=R, red_variant=args.red_variant, **rv)
+        bd = tp4.CtappBoundary(M, 256, 256, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, R=R, **rv)
         bd.inbox.normal_()
         ext = bd.ext
         times = []
@@ -331,7 +331,7 @@ def run_reducer(args, rank, world, local_rank):
             link = (t - 1) * S / (ms * 1e-3) / 1e9
             rows[R] = {"ms": round(ms, 4), "hbm_GBs": round(hbm, 1), "hbm_frac_of_measured_peak": round(hbm / peak_hbm, 4),
                        "nvlink_egress_GBs": round(link, 1), "nvlink_frac_of_770": round(link / 770.0, 4)}
-        print(json.dumps({"workload": f"owner reducer alone (variant {args.red_variant}), TP{t}, M={M}, n1=8192, push={'nvls' if args.protocol == 'v3' and t > 1 else 'unicast'}",
+        print(json.dumps({"workload": f"owner reducer alone, TP{t}, M={M}, n1=8192, push={'nvls' if args.protocol == 'v3' and t > 1 else 'unicast'}",
                           "bytes_per_rank": {"hbm_read": (t + 1) * S, "hbm_write": t * S, "nvlink_egress": (t - 1) * S}, "by_R": rows}), flush=True)
     tp4.barrier()
 
@@ -421,7 +421,6 @@ def main():
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
     ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = on at TP8 only: it measured neutral to slightly slower at TP2 and TP4")
     ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")
-    ap.add_argument("--red-variant", type=int, default=1, help="boundary / reducer: 1 = loads through registers, 2 = cp.async-staged through shared memory")
     ap.add_argument("--red-blocks", type=int, default=-1, help="boundary: reducer CTAs (-1 = R; with --R 0 they share SMs with the GEMMs' CTAs)")
     ap.add_argument("--red-threads", type=int, default=1024, help="boundary: threads per reducer CTA (<= 512 to share an SM with a GEMM CTA)")
     ap.add_argument("--no-sustained", action="store_true", help="chain: keep the one-second sustained loop as short as the timed region (profiler captures)")

@@ -317,27 +317,6 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
   return 0;
 }
 
-template <int W> static int launch_reduce_staged(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
-  using C = RedStaged<W>;
-  if (p.x_mc) {
-    CU_OK(cudaFuncSetAttribute(tp_reduce_staged_kernel<W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    tp_reduce_staged_kernel<W, true><<<blocks, threads, C::kSmemBytes, s>>>(p);
-  } else {
-    CU_OK(cudaFuncSetAttribute(tp_reduce_staged_kernel<W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    tp_reduce_staged_kernel<W, false><<<blocks, threads, C::kSmemBytes, s>>>(p);
-  }
-  CU_OK(cudaGetLastError());
-  return 0;
-}
-static int launch_reduce_staged_any(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
-  switch (p.world) {
-    case 1: return launch_reduce_staged<1>(p, blocks, threads, s);
-    case 2: return launch_reduce_staged<2>(p, blocks, threads, s);
-    case 4: return launch_reduce_staged<4>(p, blocks, threads, s);
-    default: return launch_reduce_staged<8>(p, blocks, threads, s);
-  }
-}
-
 static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
   switch (p.world) {
     case 1: return launch_reduce<1>(p, blocks, threads, s);
@@ -350,7 +329,7 @@ static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cud
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 5; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
+int ctapp_abi_version(void) { return 4; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;
@@ -418,13 +397,6 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, RedRows<2>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, RedRows<4>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, RedRows<8>::value, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<1, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<2, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<4, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<8, false>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<2, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<4, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_staged_kernel<8, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 4, true, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 4, true, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 4, true, true>));
@@ -603,11 +575,6 @@ int ctapp_tp_reduce(const ctapp_tp_reduce_args* a, int device, void* stream) {
   ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);
   GUARD(device);
   if (a->M == 0) return 0;
-  if (a->staged) {
-    ARG(a->threads <= 512, "the staged reducer runs at most 16 warps per CTA (threads %d)", a->threads);
-    ARG(!a->partials_mc, "the staged reducer reads the inbox; the in-switch reduction has none");
-    return launch_reduce_staged_any(p, a->blocks, a->threads, static_cast<cudaStream_t>(stream));
-  }
   return launch_reduce_any(p, a->blocks, a->threads, static_cast<cudaStream_t>(stream));
 }
 
@@ -622,8 +589,7 @@ int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* str
   // what this variant does not do is refused, not dropped: a caller that set one of these would get other behaviour than it asked for
   ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc && !a->partials_mc,
       "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc / partials_mc must be NULL");
-  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all && !a->staged,
-      "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger, help_all and staged 0");
+  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger and help_all 0");
   ReduceParams p;
   if (int r = fill_reduce(a, p, false)) return r;
   ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);

@@ -103,20 +103,9 @@ __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
 //     128 row sums and then panel_flag[m] = epoch to every rank
 // LR (needs MC): the W partials are not read from the inbox but summed by the NVSwitch: one multimem.ld_reduce (fp32
 // accumulation in the switch, bf16 result) on the multicast address of the ranks' partial buffers replaces the W loads and adds.
-// STG > 0: the loads go through a private shared-memory ring of STG batches per warp (`ring`), filled with cp.async: every lane
-// copies its own 16 bytes of every source STG - 1 batches ahead and reads back only what it copied itself, so no barrier is
-// needed.  What a reducer SM moves is bounded by the bytes it has in flight; registers hold about 64 KB of them, the ring
-// up to 220 KB.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-template <int W, int ROWS, bool MC, bool LR = false, int STG = 0>
-__device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, int u, int Pr, int tiles_n, int lane, uint8_t* ring = nullptr) {
+template <int W, int ROWS, bool MC, bool LR = false>
+__device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, int u, int Pr, int tiles_n, int lane) {
   static_assert(ROWS == 1 || ROWS == 2 || ROWS == 4, "rows per batch");
-  static_assert(!(LR && STG > 0), "the in-switch reduction loads through registers");
   int j, n, q;
   unit_map(u, Pr, tiles_n, p.tail, p.order, p.swz, j, n, q);
   if (p.unit_log && lane == 0) p.unit_log[1 + atomicAdd(p.unit_log, 1)] = (j << 16) | (n << 2) | q;
@@ -137,53 +126,22 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
   size_t ioff = static_cast<size_t>(j * 128 + q * 32) * row_vecs + n * 32 + lane;
   size_t xoff0 = static_cast<size_t>(xrow0) * row_vecs + n * 32 + lane;
   const bool rsrc = p.resid != nullptr;
-  constexpr int kParts = LR ? 1 : W;
-  constexpr int kSlot = ROWS * (kParts + 1) * 512;      // bytes of one batch in the ring: ROWS x (sources + residual) x 32 lanes x 16
-  constexpr int kBatches = 32 / ROWS;
-  const size_t ioff_u = ioff, xoff_u = xoff0;
-  auto prefetch = [&](int b) {     // batch b of this unit -> ring slot b % STG
-    uint8_t* slot = ring + (b % (STG > 0 ? STG : 1)) * kSlot + lane * 16;
-    const size_t io = ioff_u + static_cast<size_t>(b * ROWS) * row_vecs, xo = xoff_u + static_cast<size_t>(b * ROWS) * row_vecs;
-#pragma unroll
-    for (int rr = 0; rr < ROWS; rr++) {
-#pragma unroll
-      for (int s = 0; s < kParts; s++) cp_async16(slot + (rr * (kParts + 1) + s) * 512, p.inbox[s] + io + rr * row_vecs);
-      if (rsrc) cp_async16(slot + (rr * (kParts + 1) + kParts) * 512, p.resid + xo + rr * row_vecs);
-    }
-    cp_async_commit();
-  };
-  if (STG > 0) {
-#pragma unroll
-    for (int b = 0; b < STG - 1; b++) prefetch(b);
-  }
 #pragma unroll 1
   for (int r = 0; r < 32; r += ROWS, ioff += static_cast<size_t>(ROWS) * row_vecs, xoff0 += static_cast<size_t>(ROWS) * row_vecs) {
+    constexpr int kParts = LR ? 1 : W;
     uint4 part[ROWS][kParts], res[ROWS];
-    if (STG > 0) {
-      const int b = r / ROWS;
-      if (b + STG - 1 < kBatches) prefetch(b + STG - 1); else cp_async_commit();     // one group per iteration keeps the count uniform
-      cp_async_wait<(STG > 0 ? STG - 1 : 0)>();                                       // batch b (this lane's copies) has landed
-      const uint8_t* slot = ring + (b % (STG > 0 ? STG : 1)) * kSlot + lane * 16;
 #pragma unroll
-      for (int rr = 0; rr < ROWS; rr++) {
+    for (int rr = 0; rr < ROWS; rr++) {
+      if (LR) {
+        part[rr][0] = multimem_ld_reduce_bf16x8(p.partials_mc + xoff0 + rr * row_vecs);   // the partials sit at x's own offsets
+      } else {
 #pragma unroll
-        for (int s = 0; s < kParts; s++) part[rr][s] = *reinterpret_cast<const uint4*>(slot + (rr * (kParts + 1) + s) * 512);
-        if (rsrc) res[rr] = *reinterpret_cast<const uint4*>(slot + (rr * (kParts + 1) + kParts) * 512);
+        for (int s = 0; s < kParts; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
       }
-    } else {
+    }
+    if (rsrc) {
 #pragma unroll
-      for (int rr = 0; rr < ROWS; rr++) {
-        if (LR) {
-          part[rr][0] = multimem_ld_reduce_bf16x8(p.partials_mc + xoff0 + rr * row_vecs);   // the partials sit at x's own offsets
-        } else {
-#pragma unroll
-          for (int s = 0; s < kParts; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
-        }
-      }
-      if (rsrc) {
-#pragma unroll
-        for (int rr = 0; rr < ROWS; rr++) res[rr] = __ldg(p.resid + xoff0 + rr * row_vecs);
-      }
+      for (int rr = 0; rr < ROWS; rr++) res[rr] = __ldg(p.resid + xoff0 + rr * row_vecs);
     }
     float ss[ROWS];
 #pragma unroll
@@ -269,8 +227,8 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
 // next unit from the shared counter instead (first / stride unused), which lets CTAs of another kernel join in.
 // kOnlyReady (helpers from another kernel): a warp takes a unit only while the NEXT unclaimed unit's tile has already arrived,
 // i.e. while the dedicated reducer CTAs are behind the producers; once the reducers keep pace it leaves instead of waiting.
-template <int W, int ROWS, bool MC, bool kOnlyReady = false, bool LR = false, int STG = 0>
-__device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, int first, int stride, int lane, uint8_t* ring = nullptr) {
+template <int W, int ROWS, bool MC, bool kOnlyReady = false, bool LR = false>
+__device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, int first, int stride, int lane) {
   const int P = p.M / 128;
   const int Pr = P > p.rank ? (P - 1 - p.rank) / W + 1 : 0;
   const int tiles_n = p.n1 / 256;
@@ -291,7 +249,7 @@ __device__ __forceinline__ void reduce_units(const ReduceParams& p, int epoch, i
     return __shfl_sync(0xffffffffu, v, 0);
   };
   for (int u = p.unit_ctr ? claim() : first; u < U; u = p.unit_ctr ? claim() : u + stride)
-    if (!reduce_unit<W, ROWS, MC, LR, STG>(p, epoch, u, Pr, tiles_n, lane, ring)) return;   // a producer never delivered: the host reads the status
+    if (!reduce_unit<W, ROWS, MC, LR>(p, epoch, u, Pr, tiles_n, lane)) return;   // a producer never delivered: the host reads the status
 }
 
 // rows per batch: as many as the register file of a 1024-thread CTA allows (64 registers per thread)
@@ -305,25 +263,6 @@ __global__ void __launch_bounds__(1024, 1) tp_reduce_kernel(const ReduceParams p
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   reduce_units<W, ROWS, MC, false, LR>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x) * nwarps, lane);
-}
-
-// The staged form of the reducer kernel: 16 warps per CTA, each with a private ring of STG batches in dynamic shared memory.
-template <int W> struct RedStaged {
-  static constexpr int kRows = W >= 4 ? 1 : (W == 2 ? 2 : 4);
-  static constexpr int kStages = W >= 8 ? 3 : (W >= 4 ? 5 : (W == 2 ? 4 : 3));
-  static constexpr int kWarps = 16;
-  static constexpr int kSlot = kRows * (W + 1) * 512;
-  static constexpr unsigned kSmemBytes = kWarps * kStages * kSlot;
-};
-template <int W, bool MC>
-__global__ void __launch_bounds__(512, 1) tp_reduce_staged_kernel(const ReduceParams p) {
-  using C = RedStaged<W>;
-  extern __shared__ __align__(16) uint8_t red_ring[];
-  if (p.pdl_trigger) pdl_launch_dependents();
-  const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  reduce_units<W, C::kRows, MC, false, false, C::kStages>(p, epoch, warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
-                                                         static_cast<int>(gridDim.x) * nwarps, lane, red_ring + warp * C::kStages * C::kSlot);
 }
 
 // Consumer CTAs helping the owner reducer (any CTA shape): every warp claims units while there are units whose tiles have

@@ -24,7 +24,7 @@ SOURCES = ["ctapp_b200.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-ABI_VERSION = 5
+ABI_VERSION = 4
 STATUS_INTS = 8
 MAX_WORLD = 8
 
@@ -109,7 +109,7 @@ class TpReduceArgs(C.Structure):
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("order", C.c_int), ("swz", C.c_int), ("unit_ctr", C.c_void_p),
                 ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("help_all", C.c_int), ("trace", C.c_void_p),
-                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("partials_mc", C.c_void_p), ("staged", C.c_int)]
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("partials_mc", C.c_void_p)]
 
 
 _SIGS = {
@@ -407,7 +407,7 @@ class Tp4Module:
     @staticmethod
     def _reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                      rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=1, swz=1, unit_ctr=0, unit_log=None, pdl_trigger=0,
-                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0, partials_mc_ptr=0, staged=0):
+                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0, partials_mc_ptr=0):
         """The owner reducer's argument block (``ctapp_tp_reduce_args``), shared by tp4_reduce, tp4_reduce_noalloc and the mode-8
         consumer.  ``panels_per_owner`` is required: the flags are indexed with it, and a wrong value aliases the sources."""
         if panels_per_owner <= 0:
@@ -424,7 +424,7 @@ class Tp4Module:
         a.unit_ctr, a.unit_log, a.pdl_trigger, a.help_all = _ptr(unit_ctr), _ptr(unit_log), int(pdl_trigger), int(help_all)
         a.trace, a.status = _ptr(red_trace), _ptr(status)
         a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
-        a.partials_mc, a.staged = _ptr(partials_mc_ptr), int(staged)
+        a.partials_mc = _ptr(partials_mc_ptr)
         return a
 
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
@@ -469,15 +469,14 @@ class Tp4Module:
                    unit_ctr=0, tail_cols=0, pdl_trigger=0, n1=8192, status=None, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, unit_log=None,
                    partials_mc_ptr=0):
         """Owner reducer, protocol version 5 (``raster`` = the producer's tile order: 1 = m fastest, 2 = n fastest; ``swz`` = its
-        n-tile group size).  ``variant`` 2 = the cp.async-staged kernel (CTAs of at most 512 threads), any other value = loads
-        through registers; ``rows`` / ``stages`` / ``dsmem`` of the reference are accepted without effect."""
+        n-tile group size).  ``variant`` / ``rows`` / ``stages`` / ``dsmem`` of the reference select kernels that have one
+        counterpart here and are accepted without effect."""
         if version != 5:
             raise RuntimeError(f"tp4_reduce: version {version} is not available in this build (5)")
         a = self._reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_cnt, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                               rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=2 if raster == 2 else 1, swz=swz,
                               unit_ctr=unit_ctr, unit_log=unit_log, pdl_trigger=pdl_trigger, red_trace=red_trace, x_mc_ptr=x_mc_ptr,
-                              rowss_mc_ptr=rowss_mc_ptr, panel_flag_mc_ptr=panel_flag_mc_ptr, partials_mc_ptr=partials_mc_ptr,
-                              staged=int(variant == 2))
+                              rowss_mc_ptr=rowss_mc_ptr, panel_flag_mc_ptr=panel_flag_mc_ptr, partials_mc_ptr=partials_mc_ptr)
         dev = tile_cnt.device.index
         _check(self.lib.ctapp_tp_reduce(C.byref(a), dev, _stream(dev)))
 

@@ -249,12 +249,6 @@ class CtappBoundary:
             raise ValueError("R=0 (no SMs set aside for the reducer) needs red_blocks (reducer CTAs sharing SMs with the GEMMs) or steal=True")
         self.sms = self.qkv_sms = self.nsm - self.R
         self.red_threads, self.red_blocks = red_threads, self.R if red_blocks is None else int(red_blocks)
-        # reducer kernel: 1 = loads through registers; 2 = cp.async-staged through shared memory (CTAs of at most 512 threads)
-        if red_variant not in (1, 2):
-            raise ValueError(f"red_variant {red_variant}: 1 (register loads) | 2 (cp.async-staged)")
-        self.red_variant = red_variant
-        if red_variant == 2:
-            self.red_threads = min(self.red_threads, 512)
         # tile orders of the three kernels
         self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
         self.down_raster, self.down_swizzle, self.down_tail = down_raster or 1, down_swizzle, down_tail
@@ -341,7 +335,6 @@ class CtappBoundary:
             return
         self.ext.tp4_reduce(M, self.rank, self.world, 0, self.down_raster, self.red_blocks, self.buf.tile_flags, version=5,
                             epoch_dev=self.buf.epoch_dev, threads=self.red_threads, swz=self.down_swizzle, n1=self.n1,
-                            variant=1 if self.ldreduce else self.red_variant,
                             unit_ctr=self.buf.role_ctr[1:] if self.steal else 0, tail_cols=self.tail_cols(M),
                             pdl_trigger=int(self.fusion == "pdl1"), unit_log=unit_log,
                             partials_mc_ptr=self.tab["partials_mc"] if self.ldreduce else 0, **self._reducer_kwargs(M, resid, parity))

@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 5 */
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 4 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);
@@ -218,12 +218,6 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
    * bf16 of the fp32 sum, and the residual is added after that rounding: results agree with the inbox path within the
    * boundary's tolerance, not bit for bit.  Needs the NVLS pushes above; NULL = read the inbox. */
   const void* partials_mc;
-  /* 1 = the staged kernel (the reference's cp.async-staged reducer, csrc/ctapp_tp4.cuh:777-855, in this library's form): CTAs of
-   * at most 512 threads whose warps each keep a private ring of batches in shared memory, filled with cp.async several
-   * batches ahead, so that an SM has up to 220 KB of loads in flight instead of the 64 KB its registers hold.  Same units,
-   * order, arithmetic and results as the register kernel.  Not with partials_mc; ignored by mode 8 of ctapp_tp_qkv (the
-   * GEMM's CTAs have no shared memory to spare).  0 = loads through registers. */
-  int staged;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 

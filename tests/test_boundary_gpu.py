@@ -75,7 +75,7 @@ def _forward_and_check(bds, M, K, n1, N2_, seed, use_resid=True, out_ulp=0.98):
 
 
 @pytest.mark.parametrize("cta_pair,kw", [(True, {}), (True, dict(steal=True)), (False, dict(down_raster=2)), (False, dict(steal=True, down_tail=0)),
-                                         ("wide", {}), ("wide", dict(down_tail=1)), (True, dict(red_variant=2)), (False, dict(red_variant=2, down_raster=2))])
+                                         ("wide", {}), ("wide", dict(down_tail=1))])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_boundary_one_gpu_plays_all_ranks(world, cta_pair, kw):
     """``steal`` here: the dedicated reducers claim their units from the shared counter and the mode-8 consumers, launched after
@@ -232,8 +232,7 @@ def test_add_rmsnorm_baseline_kernel():
 
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("cta_pair,kw", [(True, {}), (False, {}), (True, dict(steal=True)), (True, dict(steal=True, R=0)), (False, dict(steal=True)),
-                                         (True, dict(R=0, red_blocks=48, red_threads=256)),      # reducer CTAs share SMs with the GEMMs' CTAs
-                                         (True, dict(red_variant=2))])                            # cp.async-staged reducer
+                                         (True, dict(R=0, red_blocks=48, red_threads=256))])     # last: reducer CTAs share SMs with the GEMMs' CTAs
 @pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl"), (2, "pdl1")])
 def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, kw):
     """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""

@@ -80,17 +80,16 @@ static void* driver_fn(const char* name) {
 
 // bf16 row-major matrix (rows x cols, leading dimension ld elements), box box_cols x box_rows, 128-byte swizzle
 static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
-                     bool swizzle128 = true, bool f32 = false) {
+                     bool swizzle128 = true) {
   static EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(driver_fn("cuTensorMapEncodeTiled"));
   if (!enc) return fail(-3, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(-1, "matrix base %p is not 16-byte aligned", base);
-  const int esize = f32 ? 4 : 2;
-  if ((ld * esize) % 16 != 0) return fail(-1, "leading dimension %lld is not a multiple of 16 bytes", ld);
+  if ((ld * 2) % 16 != 0) return fail(-1, "leading dimension %lld is not a multiple of 8 elements", ld);
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esize};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %dx%d)", (int)r, rows, cols, ld, box_cols, box_rows);
@@ -215,7 +214,7 @@ __global__ void chain_reset_kernel(Queue q, int* sb, const int* pristine, int sb
 
 template <int W> static int launch_reduce(const ReduceParams& p, int blocks, int threads, cudaStream_t s) {
   constexpr int R = RedRows<W>::value;
-  if (p.partials_mc) tp_reduce_kernel<W, 2, true, true><<<blocks, threads, 0, s>>>(p);     // two reduced loads per row, two rows in flight
+  if (p.partials_mc) tp_reduce_kernel<W, 4, true, true><<<blocks, threads, 0, s>>>(p);     // one reduced load per row: four rows in flight
   else if (p.x_mc) tp_reduce_kernel<W, R, true><<<blocks, threads, 0, s>>>(p);
   else tp_reduce_kernel<W, R><<<blocks, threads, 0, s>>>(p);
   CU_OK(cudaGetLastError());
@@ -312,7 +311,7 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
   if (a->partials_mc) {
     ARG(p.x_mc, "the in-switch reduction (partials_mc) needs the NVLS pushes too (x_mc, rowss_mc, panel_flag_mc)");
     ARG(!a->unit_ctr || !a->help_all, "the in-switch reduction is not available to helping consumer CTAs");
-    p.partials_mc = static_cast<const float4*>(a->partials_mc);
+    p.partials_mc = static_cast<const uint4*>(a->partials_mc);
   }
   p.limit_ns = limit_ns();
   return 0;
@@ -330,7 +329,7 @@ static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cud
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 5; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
+int ctapp_abi_version(void) { return 4; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;
@@ -398,9 +397,9 @@ int ctapp_preload(int device) {
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, RedRows<2>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, RedRows<4>::value, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, RedRows<8>::value, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 2, true, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 2, true, true>));
-  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 2, true, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<2, 4, true, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<4, 4, true, true>));
+  CU_OK(cudaFuncGetAttributes(&a, tp_reduce_kernel<8, 4, true, true>));
   CU_OK(cudaFuncGetAttributes(&a, tp_step_kernel));
   CU_OK(cudaFuncGetAttributes(&a, add_rmsnorm_kernel));
   CU_OK(cudaFuncGetAttributes(&a, gemm2_kernel<false>));
@@ -515,12 +514,11 @@ int ctapp_tp_down(const ctapp_tp_down_args* a, int device, void* stream) {
         "inbox slot of %d rows / %d panels per owner does not fit M=%d on %d ranks (panels_per_owner must be >= ceil(M/128/world) and its rows <= dst_rows)",
         a->dst_rows, a->panels_per_owner, a->M, a->world);
     ARG(!a->dst_global || a->dst_rows >= a->M, "dst_global: every destination must hold all M=%d rows (dst_rows %d)", a->M, a->dst_rows);
-    ARG(!a->dst_f32 || (pair && a->dst_global), "dst_f32 (fp32 partial buffers) needs the CTA-pair kernel and dst_global");
-    p.mode = kModeTpProducer; p.dst_global = a->dst_global != 0; p.dst_f32 = a->dst_f32 != 0;
+    p.mode = kModeTpProducer; p.dst_global = a->dst_global != 0;
     p.world = a->world; p.rank = a->rank; p.ppo = a->panels_per_owner;
     for (int d = 0; d < a->world; d++) {
       ARG(a->dst_ptrs[d] && a->peer_tile_flags[d], "missing destination %d", d);
-      if (int r = make_tmap(&p.tmD[d], a->dst_ptrs[d], a->dst_rows, a->N, a->N, a->dst_f32 ? 32 : kStoreCols, kStageRows, true, a->dst_f32 != 0)) return r;
+      if (int r = make_tmap(&p.tmD[d], a->dst_ptrs[d], a->dst_rows, a->N, a->N, kStoreCols, kStageRows)) return r;
       p.peer_tile_flags[d] = a->peer_tile_flags[d];
     }
   }

@@ -325,27 +325,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           if (lane == 0) { if (leader) mbar_arrive_cluster_local(tempty + a); else mbar_arrive_remote(mapa_u32(tempty + a, 0)); }
         }
         if (!valid) continue;
-        if (!kAct && p.dst_f32) {
-          // fp32 destination (the partial buffers of the in-switch reduction): the accumulator goes out unrounded, 32 columns
-          // (one 128-byte row of floats) per staging buffer, two stores per 64-column chunk
-#pragma unroll
-          for (int h = 0; h < 2; h++) {
-            uint8_t* fbuf = stage_buf + (cbuf & 1u) * (kStageRows * kStoreCols * 2);
-            cbuf++;
-            if (lane == 0) bulk_wait_read<1>();
-            __syncwarp();
-#pragma unroll
-            for (int q = 0; q < 8; q++)
-              *reinterpret_cast<uint4*>(fbuf + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(v[h][4 * q], v[h][4 * q + 1], v[h][4 * q + 2], v[h][4 * q + 3]);
-            fence_proxy_async_shared();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(tmD, fbuf, n * BN + c * kStoreCols + h * 32, drow + lane_base);
-              bulk_commit();
-            }
-          }
-          continue;
-        }
         uint8_t* buf = stage_buf + (cbuf & 1u) * (kStageRows * kStoreCols * 2);
         cbuf++;
         if (lane == 0) bulk_wait_read<1>();

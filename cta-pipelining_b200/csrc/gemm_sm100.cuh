@@ -62,7 +62,6 @@ struct alignas(64) GemmParams {
   int chunk_kblocks, chunk_cols, chunk_value;
   // tensor-parallel boundary
   int world, rank, ppo;
-  int dst_f32;                       // producer (CTA-pair kernel): the destinations are fp32 matrices; tmD are fp32 maps with 32 x 32 boxes
   int dst_global;                    // producer: a tile's destination rows are its own rows (every tmD describes an (M, N) buffer, e.g.
                                      // this rank's partial buffer for the in-switch reduction) instead of the owner's inbox rows
   int* peer_tile_flags[kMaxWorld];

@@ -141,14 +141,6 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
   return v;
 }
 
-// 4 fp32 from every GPU of the group, summed inside the switch
-__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc) {
-  float4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
-  return v;
-}
-
 // ------------------------------------------------------------------------------------------ bounded waits
 // Records the first give-up of a launch in the status buffer (first writer wins; later ones only count).
 __device__ __forceinline__ void report_status(int* status, int code, int what, int expected, int seen) {

@@ -37,9 +37,9 @@ struct ReduceParams {
   uint4* x_mc;
   float* rowss_mc;
   int* panel_flag_mc;
-  // in-switch reduction: multicast address of the ranks' partial-sum buffers ((M, n1) FP32, every rank's own producer output at
+  // in-switch reduction: multicast address of the ranks' partial-sum buffers ((M, n1) bf16, every rank's own producer output at
   // the same offset); null = the partials are read from the local inbox slices
-  const float4* partials_mc;
+  const uint4* partials_mc;
 };
 
 // Unit u -> (owned panel j, n-tile, quarter).  The order follows the producer's tile order so that units become ready in
@@ -101,9 +101,8 @@ __device__ __forceinline__ float sumsq_bf16x8(uint4 o) {
 //     by ROWS lanes at once
 //   * lane 0 orders everything above before the panel's arrival count; the warp that completes the panel pushes the panel's
 //     128 row sums and then panel_flag[m] = epoch to every rank
-// LR (needs MC): the W partials are not read from the inbox but summed by the NVSwitch: the producers keep their tiles as fp32
-// in their own partial buffers, and two multimem.ld_reduce.add.v4.f32 on the buffers' multicast address return the 8 cross-rank
-// sums of a lane's 16 output bytes (fp32 in, fp32 out: nothing is rounded before the residual is added).
+// LR (needs MC): the W partials are not read from the inbox but summed by the NVSwitch: one multimem.ld_reduce (fp32
+// accumulation in the switch, bf16 result) on the multicast address of the ranks' partial buffers replaces the W loads and adds.
 template <int W, int ROWS, bool MC, bool LR = false>
 __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, int u, int Pr, int tiles_n, int lane) {
   static_assert(ROWS == 1 || ROWS == 2 || ROWS == 4, "rows per batch");
@@ -131,12 +130,10 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
   for (int r = 0; r < 32; r += ROWS, ioff += static_cast<size_t>(ROWS) * row_vecs, xoff0 += static_cast<size_t>(ROWS) * row_vecs) {
     constexpr int kParts = LR ? 1 : W;
     uint4 part[ROWS][kParts], res[ROWS];
-    float4 psum[LR ? ROWS : 1][2];
 #pragma unroll
     for (int rr = 0; rr < ROWS; rr++) {
-      if (LR) {      // the partials sit at x's own (row, column) position: 8 fp32 = two 16-byte vectors per lane
-        psum[rr][0] = multimem_ld_reduce_f32x4(p.partials_mc + 2 * (xoff0 + rr * row_vecs));
-        psum[rr][1] = multimem_ld_reduce_f32x4(p.partials_mc + 2 * (xoff0 + rr * row_vecs) + 1);
+      if (LR) {
+        part[rr][0] = multimem_ld_reduce_bf16x8(p.partials_mc + xoff0 + rr * row_vecs);   // the partials sit at x's own offsets
       } else {
 #pragma unroll
         for (int s = 0; s < kParts; s++) part[rr][s] = __ldcg(p.inbox[s] + ioff + rr * row_vecs);
@@ -153,12 +150,8 @@ __device__ __forceinline__ bool reduce_unit(const ReduceParams& p, int epoch, in
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         float lo = -0.0f, hi = -0.0f;
-        if (LR) {
-          lo = (&psum[rr][i >> 1].x)[(i & 1) * 2]; hi = (&psum[rr][i >> 1].x)[(i & 1) * 2 + 1];
-        } else {
 #pragma unroll
-          for (int s = 0; s < kParts; s++) { const uint32_t w = (&part[rr][s].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
-        }
+        for (int s = 0; s < kParts; s++) { const uint32_t w = (&part[rr][s].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
         if (rsrc) { const uint32_t w = (&res[rr].x)[i]; lo = add_bf16_lo(lo, w); hi = add_bf16_hi(hi, w); }
         o[i] = pack_bf16x2(lo, hi);
       }

@@ -24,7 +24,7 @@ SOURCES = ["ctapp_b200.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-ABI_VERSION = 5
+ABI_VERSION = 4
 STATUS_INTS = 8
 MAX_WORLD = 8
 
@@ -92,7 +92,7 @@ class TpDownArgs(C.Structure):
                 ("epoch", C.c_int), ("epoch_dev", C.c_void_p), ("dst_ptrs", C.c_void_p * MAX_WORLD), ("dst_rows", C.c_int),
                 ("peer_tile_flags", C.c_void_p * MAX_WORLD), ("panels_per_owner", C.c_int), ("sms", C.c_int),
                 ("pdl_trigger", C.c_int), ("pdl", C.c_int), ("tail_cols", C.c_int), ("trace", C.c_void_p), ("status", C.c_void_p),
-                ("cta_pair", C.c_int), ("dst_global", C.c_int), ("dst_f32", C.c_int), ("tile_log", C.c_void_p)]
+                ("cta_pair", C.c_int), ("dst_global", C.c_int), ("tile_log", C.c_void_p)]
 
 
 class TpQkvArgs(C.Structure):
@@ -385,7 +385,7 @@ class Tp4Module:
     def tp4_down(self, A, W, D, raster, swizzle, mode, rank, world, epoch, tile_cnt_mc=0, tile_cnt=None, partials_mc=0, x_mc=0,
                  resid=None, rowss_mc=0, panel_cnt_mc=0, sms=0, epoch_dev=None, rowss_mc_base=0, rowss_stride=0, d_ptr=0,
                  dst_ptrs=(), dst_rows=0, peer_tile_flags=(), panels_per_owner=0, pdl_trigger=0, trace=0, tail_cols=0, pdl=0, status=None, cta_pair=0,
-                 tile_log=None, dst_global=0, dst_f32=0):
+                 tile_log=None, dst_global=0):
         A, W = _bf16_matrix(A, "A"), _bf16_matrix(W, "W")
         if mode not in (0, 7):
             raise RuntimeError(f"tp4_down: mode {mode} is not available in this build (0 | 7)")
@@ -400,7 +400,7 @@ class Tp4Module:
         a.dst_ptrs, a.dst_rows = _ptr_array(dst_ptrs), int(dst_rows)
         a.peer_tile_flags, a.panels_per_owner = _ptr_array(peer_tile_flags), int(panels_per_owner)
         a.sms, a.pdl_trigger, a.pdl, a.tail_cols = int(sms), int(pdl_trigger), int(pdl), int(tail_cols)
-        a.trace, a.status, a.cta_pair, a.tile_log, a.dst_global, a.dst_f32 = _ptr(trace), _ptr(status), int(cta_pair), _ptr(tile_log), int(dst_global), int(dst_f32)
+        a.trace, a.status, a.cta_pair, a.tile_log, a.dst_global = _ptr(trace), _ptr(status), int(cta_pair), _ptr(tile_log), int(dst_global)
         dev = A.device.index
         _check(self.lib.ctapp_tp_down(C.byref(a), dev, _stream(dev)))
 

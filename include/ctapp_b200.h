@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 5 */
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 4 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);
@@ -146,8 +146,6 @@ typedef struct ctapp_tp_down_args {   /* gemm_tp4.cu:156-199 (tp4_down); modes 0
                                               producer stores locally and only the tile flag crosses the link: the layout the
                                               in-switch reduction reads (ctapp_tp_reduce_args.partials_mc; the reference's producer
                                               mode 4, csrc/ctapp_tp4.cuh:284-289) */
-  int dst_f32;                             /* mode 7 with cta_pair and dst_global: the destinations are FP32 matrices (the unrounded
-                                              accumulators are stored): what ctapp_tp_reduce_args.partials_mc sums */
   int* tile_log;                           /* NULL, or [0] = 0 on entry and room for 1 + #tiles ints: the kernel appends one packed
                                               (m << 16 | n) per tile in the order its schedulers take them (m = tile row of the
                                               schedule: 256 rows with cta_pair); with one CTA (pair) that is the tile order itself */
@@ -215,10 +213,10 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   float* rowss_mc;
   int* panel_flag_mc;
   /* In-switch reduction (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.ld_reduce): multicast address of the ranks' partial
-   * buffers, (M, n1) FP32 each, written by producers launched with dst_global and dst_f32.  The W loads and adds per 16
-   * output bytes become two multimem.ld_reduce.add.v4.f32; `inbox` is not read.  The partials are not rounded to bf16 on the
-   * way (the reference's bf16 form, ...acc::f32.v4.bf16x2, returns a bf16 that is not the nearest one on this hardware and
-   * missed the mean-error bound), at the price of twice the bytes on the link.  Needs the NVLS pushes above; NULL = read the inbox. */
+   * buffers, (M, n1) bf16 each, written by producers launched with dst_global.  The W loads and adds per output become one
+   * multimem.ld_reduce.add.acc::f32.v4.bf16x2; `inbox` is not read.  The switch's bf16 result is not always the nearest
+   * bf16 of the fp32 sum, and the residual is added after that rounding: results agree with the inbox path within the
+   * boundary's tolerance, not bit for bit.  Needs the NVLS pushes above; NULL = read the inbox. */
   const void* partials_mc;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);

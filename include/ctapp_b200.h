@@ -214,9 +214,9 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
   int* panel_flag_mc;
   /* In-switch reduction (csrc/ctapp_tp4.cuh:150-183, 458-536: multimem.ld_reduce): multicast address of the ranks' partial
    * buffers, (M, n1) bf16 each, written by producers launched with dst_global.  The W loads and adds per output become one
-   * multimem.ld_reduce.add.acc::f32.v4.bf16x2; `inbox` is not read.  The switch's bf16 result is not always the nearest
-   * bf16 of the fp32 sum, and the residual is added after that rounding: results agree with the inbox path within the
-   * boundary's tolerance, not bit for bit.  Needs the NVLS pushes above; NULL = read the inbox. */
+   * multimem.ld_reduce.add.acc::f32.v4.bf16x2; `inbox` is not read.  The switch returns the sum as bf16 and the residual is
+   * added after that rounding: one bf16 rounding more than the inbox path, so results agree with it within the boundary's
+   * max-error tolerance, not bit for bit (the mean error against the inbox path's rounding model doubles).  Needs the NVLS pushes above; NULL = read the inbox. */
   const void* partials_mc;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);

@@ -90,12 +90,12 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     bd = tp4.CtappBoundary(max_M, Kr, N2r, rank, world, gn, dev, protocol=protocol, max_M=max_M, n1=n1, fusion=fusion, cta_pair=cta_pair, steal=steal)
     if protocol in ("v3", "v3r") and not bd.nvls:
         return ["SKIP: no multicast address on this system"]
-    # in-switch reduction: the switch returns a bf16 that is often not the nearest one to its fp32 sum (measured: its error is
-    # one-sided, like a truncation) and the residual is added after that rounding.  x stays inside the bounds (measured max 1.7e-2,
-    # mean 9.2e-4 of the RMS) but sits up to two bf16 steps from the model, and the one-sided error adds up coherently in the
-    # consumer GEMM: out's mean error was measured at 1.9e-3 of the RMS, above the 1e-3 the other protocols are held to.  The
-    # variant is opt-in for that reason; this test pins what it does deliver (max 2e-2, mean 3e-3).
-    x_ulp, out_ulp, steps, out_mean = (0.99, 0.98, 1, 1e-3) if protocol != "v3r" else (0.95, 0.85, 2, 3e-3)
+    # in-switch reduction: the switch returns the partials' sum as bf16 and the residual is added after that rounding: one bf16
+    # rounding more than the model (and the inbox path), which adds everything in fp32 and rounds once.  x stays inside the bounds
+    # (measured max 1.7e-2, mean 9.2e-4 of the RMS) but sits up to two bf16 steps from the model; out's mean error was measured
+    # at 1.9e-3 of the RMS, twice the 1e-3 the other protocols are held to against this model.  The variant is opt-in for that
+    # reason; this test pins what it does deliver (max 2e-2, mean 2.5e-3).
+    x_ulp, out_ulp, steps, out_mean = (0.99, 0.98, 1, 1e-3) if protocol != "v3r" else (0.95, 0.85, 2, 2.5e-3)
     for it, M in enumerate(Ms):
         Wd, gamma, Wq = ob.make_weights(seed=1 + it, K=K, N2_=N2_, n1=n1)
         wd, _, wqf = ob.shard_weights(Wd, Wq, gamma, rank, world)

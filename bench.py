@@ -195,7 +195,7 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     resid = torch.randn(M, tp4.N1, generator=g).to(torch.bfloat16).to(dev)
     iters, warm = max(args.steps, 10), max(args.warmup, 3)
     res = {}
-    steal = bool(args.steal) if args.steal in (0, 1) else t >= 8
+    steal = args.steal == 1
     bd = tp4.CtappBoundary(M, Kr, N2r, rank, t, None, dev, protocol=args.protocol if t > 1 else "v5", max_M=M, fusion=args.fusion,
                            R=None if args.R < 0 else args.R, steal=steal, red_blocks=args.red_blocks if args.red_blocks >= 0 else None,
                            red_threads=args.red_threads, cta_pair={1: "wide", 0: "narrow"}.get(args.down_wide, True), **akw)
@@ -419,7 +419,7 @@ def main():
                     "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8: 'head' "
                     "measured 0.7-0.9 %% slower on 2 GPUs and 0.2-1 %% slower on 4)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
-    ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = on at TP8 only: it measured neutral to slightly slower at TP2 and TP4")
+    ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = off (the library's default): it measured neutral to slightly slower at TP2 and TP4")
     ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")
     ap.add_argument("--red-blocks", type=int, default=-1, help="boundary: reducer CTAs (-1 = R; with --R 0 they share SMs with the GEMMs' CTAs)")
     ap.add_argument("--red-threads", type=int, default=1024, help="boundary: threads per reducer CTA (<= 512 to share an SM with a GEMM CTA)")
@@ -430,7 +430,7 @@ def main():
     ap.add_argument("--baselines", default="stock", choices=["stock", "strong"],
                     help="boundary: strong = also torch's multimem all-reduce and async-TP (fused matmul + reduce-scatter) boundaries")
     ap.add_argument("--shape", default="B", choices=["A", "B"], help="boundary: B = down-proj -> QKV (headline), A = o_proj -> gate_up")
-    ap.add_argument("--R", type=int, default=-1, help="boundary: SMs reserved for the owner reducer (-1 = library default: 4 up to TP2, 8 from TP4; 0 with "
+    ap.add_argument("--R", type=int, default=-1, help="boundary: SMs reserved for the owner reducer (-1 = library default: 4 up to TP2, 8 at TP4, 12 at TP8; 0 with "
                     "--steal 1 = none, the consumer's CTAs do the reduction)")
     args = ap.parse_args()
     if args.m is None:

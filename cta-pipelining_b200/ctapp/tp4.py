@@ -240,9 +240,12 @@ class CtappBoundary:
         self.use_resid, self.protocol, self.v5 = resid, bool(protocol), bool(protocol)
         self.use_graph, self.graph_bind = use_graph, bool(graph_bind)
         self.fusion, self.steal = fusion, bool(steal)
-        # SM split: R SMs are left to the owner reducer (measured on B200 at M=4096: TP2 best with 4, TP4 and TP8 with 8)
+        # SM split: R SMs are left to the owner reducer.  Measured on B200 at M=4096: TP2 best with 4; TP4 0.515 / 0.509 / 0.525 ms
+        # with 8 / 12 / 16; TP8 0.519 / 0.378 ms with 4 / 8, i.e. 0.237 + 1.13 / R (a reducer SM moves about 80 GB/s whatever it
+        # runs, and at TP8 the two GEMMs are over before 8 such SMs are through): 12 is where that line meets the cost of the SMs
+        # taken from the GEMMs
         self.nsm = torch.cuda.get_device_properties(self.dev).multi_processor_count
-        self.R = (8 if world >= 4 else 4) if R is None else int(R)
+        self.R = (4 if world <= 2 else 8 if world <= 4 else 12) if R is None else int(R)
         # R = 0 gives both GEMMs every SM.  The reduction is then done by ``red_blocks`` small reducer CTAs that share SMs with
         # the GEMMs' CTAs (a GEMM CTA leaves more than half of an SM's registers and nearly all its thread slots free; choose
         # ``red_threads`` <= 512 so that both fit), by the consumer's CTAs (``steal``), or by both

@@ -173,3 +173,19 @@ def test_doubled_links_schedule_has_no_cycle_and_no_set_reuse():
             assert ("reset", g, e + 2) in deps[("gemm", g - 1, e + 2)]
     # at most two steps of a link are in flight: the producer's step e+2 needs the consumer's step e to be over
     assert all(pos[("gemm", g, e)] < pos[("gemm", g - 1, e + 2)] for g in range(1, L) for e in range(1, E - 1))
+
+
+def test_producer_tile_choice_and_reducer_sm_defaults():
+    """Host rules of ``CtappBoundary`` that need no GPU: the producer runs on 256 x 512 tiles only up to TP2 and only when every
+    CTA pair still gets one; forced choices win; one CTA per tile stays one CTA per tile."""
+    import types
+    from ctapp.tp4 import CtappBoundary
+    def pick(world, M, n1=8192, cta_pair=1, forced=None, sms=144):
+        fake = types.SimpleNamespace(cta_pair=cta_pair, n1=n1, world=world, sms=sms, _down_wide=forced)
+        return CtappBoundary.down_pair(fake, M)
+    assert pick(2, 4096) == 2 and pick(1, 4096) == 2          # 16 x 16 tiles >= 72 pairs
+    assert pick(2, 1024) == 1                                 # 4 x 16 tiles < 72 pairs
+    assert pick(4, 4096) == 1 and pick(8, 8192) == 1          # coarser tiles reach the reducer later: narrow from TP4
+    assert pick(4, 4096, forced=True) == 2 and pick(2, 4096, forced=False) == 1
+    assert pick(2, 4096, n1=768) == 1                         # hidden size not a multiple of 512
+    assert pick(2, 4096, cta_pair=0) == 0

@@ -183,6 +183,8 @@ def boundary_record(args, rank, world, dev, M=None, with_eager=True):
     M = M or args.m
     t = world
     Kr, N2r = (tp4.K_FFN // t, tp4.N2 // t) if args.shape == "B" else (8192 // t, 57344 // t)
+    if args.shard_as:      # the per-rank shapes of a wider tensor-parallel group on this many GPUs (a TP8 rank's GEMMs with a TP4 exchange)
+        Kr, N2r = tp4.K_FFN // args.shard_as, tp4.N2 // args.shard_as
     kfull = Kr * t
     akw = {} if args.shape == "B" else dict(qkv_raster=3, qkv_swizzle=4, down_tail=tp4.N1 // 256)
     g = torch.Generator().manual_seed(0)
@@ -420,6 +422,7 @@ def main():
                     "measured 0.7-0.9 %% slower on 2 GPUs and 0.2-1 %% slower on 4)")
     ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
     ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = off (the library's default): it measured neutral to slightly slower at TP2 and TP4")
+    ap.add_argument("--shard-as", type=int, default=0, help="boundary: use the per-rank GEMM shapes of this tensor-parallel degree (0 = the launch's own)")
     ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")
     ap.add_argument("--red-blocks", type=int, default=-1, help="boundary: reducer CTAs (-1 = R; with --R 0 they share SMs with the GEMMs' CTAs)")
     ap.add_argument("--red-threads", type=int, default=1024, help="boundary: threads per reducer CTA (<= 512 to share an SM with a GEMM CTA)")

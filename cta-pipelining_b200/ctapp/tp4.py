@@ -241,9 +241,9 @@ class CtappBoundary:
         self.use_graph, self.graph_bind = use_graph, bool(graph_bind)
         self.fusion, self.steal = fusion, bool(steal)
         # SM split: R SMs are left to the owner reducer.  Measured on B200 at M=4096: TP2 best with 4; TP4 0.515 / 0.509 / 0.525 ms
-        # with 8 / 12 / 16; TP8 0.519 / 0.378 ms with 4 / 8, i.e. 0.237 + 1.13 / R (a reducer SM moves about 80 GB/s whatever it
-        # runs, and at TP8 the two GEMMs are over before 8 such SMs are through): 12 is where that line meets the cost of the SMs
-        # taken from the GEMMs
+        # with 8 / 12 / 16; TP8 0.519 / 0.378 ms with 4 / 8 (a reducer SM moves about 80 GB/s whatever it runs, and at TP8 the
+        # two GEMMs are over before 8 such SMs are through); with a TP8 rank's GEMM shapes on 4 GPUs 0.347 / 0.311 / 0.307 / 0.312 ms
+        # with 8 / 12 / 16 / 24
         self.nsm = torch.cuda.get_device_properties(self.dev).multi_processor_count
         self.R = (4 if world <= 2 else 8 if world <= 4 else 12) if R is None else int(R)
         # R = 0 gives both GEMMs every SM.  The reduction is then done by ``red_blocks`` small reducer CTAs that share SMs with

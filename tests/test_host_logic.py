@@ -189,3 +189,25 @@ def test_producer_tile_choice_and_reducer_sm_defaults():
     assert pick(4, 4096, forced=True) == 2 and pick(2, 4096, forced=False) == 1
     assert pick(2, 4096, n1=768) == 1                         # hidden size not a multiple of 512
     assert pick(2, 4096, cta_pair=0) == 0
+
+
+def test_handover_model_orders_and_floor():
+    """The timing model of a k-chunk link walks the same tile order as the host code, never ends before the producer plus one
+    chunk, reproduces the figures quoted beside the measurements, and shows the lag behind a longer producer wave."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "cta-pipelining_b200", "bench"))
+    import handover_model as hm
+    from ctapp.pipeline import producer_order
+    for tm, tn, g in [(16, 32, 4), (7, 5, 2), (3, 4, 8)]:
+        want = producer_order(tm * tn, tn, g).tolist()
+        assert [m * tn + n for m, n in hm.grouped_order(tm, tn, g)] == want
+    for M in (1024, 4096, 8192):
+        for g in (1, 2, 4, 8):
+            tp, end = hm.link(M, group_rows=g)
+            assert end >= tp + 97.0 / 32 - 1e-9
+    assert [round(hm.link(M, group_rows=4)[1]) for M in (4096, 8192, 16384)] == [438, 814, 1505]
+    # a producer on 256x512 tiles (100 us waves) that is 5 % faster per flop still hands over later than the 256x256 one
+    tp_n, end_n = hm.link(8192, group_rows=4)
+    tp_w, end_w = hm.link(8192, group_rows=4, tile_us=95.0, producer_bn=512)
+    assert tp_w < tp_n and end_w > end_n

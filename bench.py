@@ -420,7 +420,7 @@ def main():
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8: 'head' "
                     "measured 0.7-0.9 %% slower on 2 GPUs and 0.2-1 %% slower on 4)")
-    ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1"])
+    ap.add_argument("--fusion", default="pdl", choices=["none", "pdl", "pdl1", "role"])
     ap.add_argument("--steal", type=int, default=-1, help="boundary: 1 = the consumer's CTAs help the owner reducer (mode 8), 0 = off, -1 = off (the library's default): it measured neutral to slightly slower at TP2 and TP4")
     ap.add_argument("--shard-as", type=int, default=0, help="boundary: use the per-rank GEMM shapes of this tensor-parallel degree (0 = the launch's own)")
     ap.add_argument("--down-wide", type=int, default=-1, help="boundary: 1 = the producer GEMM works on 256 x 512 tiles, 0 = on 256 x 256, -1 = the library's choice")

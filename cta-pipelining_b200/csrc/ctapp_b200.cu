@@ -303,6 +303,9 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
   p.order = a->order ? a->order : 1; p.swz = a->swz;
   p.unit_ctr = a->unit_ctr; p.unit_log = a->unit_log; p.trace = a->trace; p.status = a->status;
   p.pdl_trigger = a->pdl_trigger; p.help_all = a->help_all;
+  ARG(a->role_r >= 0 && a->role_r <= 1024 && (a->role_r == 0 || (a->role_ctr && !a->unit_ctr)),
+      "role switching: role_r %d needs role_ctr and static unit shares (unit_ctr NULL)", a->role_r);
+  p.role_ctr = a->role_r > 0 ? a->role_ctr : nullptr; p.role_r = a->role_r;
   if (a->x_mc || a->rowss_mc || a->panel_flag_mc) {   // NVLS variant: all three multicast addresses or none
     ARG(a->x_mc && a->rowss_mc && a->panel_flag_mc, "the NVLS variant needs x_mc, rowss_mc and panel_flag_mc");
     ARG(a->world >= 2, "the NVLS variant needs at least 2 ranks");
@@ -310,7 +313,7 @@ static int fill_reduce(const ctapp_tp_reduce_args* a, ReduceParams& p, bool own_
   }
   if (a->partials_mc) {
     ARG(p.x_mc, "the in-switch reduction (partials_mc) needs the NVLS pushes too (x_mc, rowss_mc, panel_flag_mc)");
-    ARG(!a->unit_ctr || !a->help_all, "the in-switch reduction is not available to helping consumer CTAs");
+    ARG((!a->unit_ctr || !a->help_all) && !a->role_r, "the in-switch reduction is not available to helping consumer CTAs");
     p.partials_mc = static_cast<const uint4*>(a->partials_mc);
   }
   p.limit_ns = limit_ns();
@@ -329,7 +332,7 @@ static int launch_reduce_any(const ReduceParams& p, int blocks, int threads, cud
 extern "C" {
 
 const char* ctapp_last_error(void) { return g_err; }
-int ctapp_abi_version(void) { return 4; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
+int ctapp_abi_version(void) { return 5; }   // 3: k-chunk flags in ctapp_chain_args; order / swz / unit_log / pdl_trigger in ctapp_tp_reduce_args (tma gone); red in ctapp_tp_qkv_args; tile_log in ctapp_tp_down_args
 int ctapp_set_wait_limit_ms(int ms) {
   ARG(ms > 0, "limit must be positive");
   g_limit_ms = ms;
@@ -556,9 +559,15 @@ int ctapp_tp_qkv(const ctapp_tp_qkv_args* a, int device, void* stream) {
     p.pdl_wait = 0;            // the per-panel flags carry the dependency on the producer grid
     if (a->mode == 8) {
       if (int r = fill_reduce(a->red, p.red, true)) return r;
-      ARG(p.red.unit_ctr, "mode 8 needs red->unit_ctr: the units are shared out through that counter");
+      ARG(p.red.unit_ctr || p.red.role_r > 0, "mode 8 needs red->unit_ctr (units shared out through that counter) or red->role_r > 0 (role switching)");
       ARG(!p.red.partials_mc, "mode 8: helping consumer CTAs read the inbox; the in-switch reduction (red->partials_mc) has no inbox");
       ARG(p.red.M == a->M && p.red.n1 == a->K, "mode 8: the reducer's shape (M=%d, n1=%d) must be this GEMM's (M=%d, K=%d)", p.red.M, p.red.n1, a->M, a->K);
+      if (p.red.role_r > 0) {   // every static share needs a CTA: a launch of fewer CTAs than role_r splits the units among those it has
+        const int nsm = sm_count(device);
+        int ctas = a->sms > 0 && a->sms < nsm ? a->sms : nsm;
+        if (pair) ctas = 2 * (ctas / 2 < p.num_tiles ? ctas / 2 : p.num_tiles); else if (ctas > p.num_tiles) ctas = p.num_tiles;
+        if (p.red.role_r > ctas) p.red.role_r = ctas;
+      }
     }
   } else {
     p.mode = a->rowss ? kModeTpConsumer : kModePlain;   // mode 0 with rowss: scale only, no waits
@@ -589,7 +598,8 @@ int ctapp_tp_reduce_noalloc(const ctapp_tp_reduce_args* a, int device, void* str
   // what this variant does not do is refused, not dropped: a caller that set one of these would get other behaviour than it asked for
   ARG(!a->x_mc && !a->rowss_mc && !a->panel_flag_mc && !a->partials_mc,
       "ctapp_tp_reduce_noalloc pushes with unicast stores only: x_mc / rowss_mc / panel_flag_mc / partials_mc must be NULL");
-  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all, "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger and help_all 0");
+  ARG(!a->unit_ctr && !a->unit_log && !a->pdl_trigger && !a->help_all && !a->role_r,
+      "ctapp_tp_reduce_noalloc assigns units statically: unit_ctr / unit_log must be NULL, pdl_trigger, help_all and role_r 0");
   ReduceParams p;
   if (int r = fill_reduce(a, p, false)) return r;
   ARG(a->threads >= 32 && a->threads <= 1024 && a->threads % 32 == 0 && a->blocks >= 1, "bad launch shape %d x %d", a->blocks, a->threads);

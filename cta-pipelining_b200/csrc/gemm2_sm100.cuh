@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
   // leader only: how many tile halves the peer has landed.  A counter, not an mbarrier: nothing stops the peer from
   // finishing two tiles before the leader's publishing warp looks, and a barrier phase that flips twice is lost.
   uint32_t* s_peer_done = reinterpret_cast<uint32_t*>(const_cast<int*>(s_abort) + 1);
+  int* s_ticket = reinterpret_cast<int*>(s_peer_done + 1);   // role switching: this CTA's ticket
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();
@@ -97,7 +98,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
   if constexpr (!kWide) {   // the wide tile is never a tensor-parallel consumer
-    if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);   // every warp, before it takes up its role
+    if (p.mode == kModeTpConsumer) {   // mode 8: every warp, before it takes up its role in the GEMM
+      if (p.red.role_r > 0) reduce_role(p.red, epoch, s_ticket);   // either CTA of a pair draws its own ticket
+      else if (p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);
+    }
   }
 
   // a give-up in one CTA stops both

@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   int* s_tile = reinterpret_cast<int*>(epi + 1);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_tile + kSchedSlots);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  int* s_ticket = const_cast<int*>(s_abort) + 1;   // role switching: this CTA's ticket
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (p.K + BK - 1) / BK;
@@ -210,7 +211,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (p.pdl_trigger) pdl_launch_dependents();
   if (p.pdl_wait) pdl_wait();
   const int epoch = p.epoch_ptr ? __ldcg(p.epoch_ptr) : p.epoch;
-  if (p.mode == kModeTpConsumer && p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);   // every warp, before it takes up its role
+  if (p.mode == kModeTpConsumer) {   // mode 8: every warp, before it takes up its role in the GEMM
+    if (p.red.role_r > 0) reduce_role(p.red, epoch, s_ticket);
+    else if (p.red.unit_ctr) reduce_help(p.red, epoch, p.red.help_all != 0);
+  }
 
   if (warp == 0) {
     // ============================================================ scheduler + TMA loader

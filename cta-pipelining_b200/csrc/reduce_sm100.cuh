@@ -40,6 +40,10 @@ struct ReduceParams {
   // in-switch reduction: multicast address of the ranks' partial-sum buffers ((M, n1) bf16, every rank's own producer output at
   // the same offset); null = the partials are read from the local inbox slices
   const uint4* partials_mc;
+  // role switching (consumer mode 8 only): the first role_r CTAs of the consumer GEMM to arrive (tickets from role_ctr, zeroed
+  // per step) ARE the owner reducer -- each runs the static share `ticket` of `role_r` -- before they take GEMM tiles
+  int* role_ctr;
+  int role_r;
 };
 
 // Unit u -> (owned panel j, n-tile, quarter).  The order follows the producer's tile order so that units become ready in
@@ -284,6 +288,25 @@ __device__ __forceinline__ void reduce_help(const ReduceParams& p, int epoch, bo
     default: CTAPP_HELP(8, 1); break;
   }
 #undef CTAPP_HELP
+}
+
+// Role switching (same integer contract as the reference's tp4_role_preamble, csrc/ctapp_tp4.cuh:913-925): every CTA of the
+// consumer GEMM draws a ticket; tickets below role_r run the owner reducer's static share ticket / role_r with all their warps,
+// the others return at once.  `s_ticket`: one word of shared memory nothing else uses.  Every thread of the CTA calls this.
+__device__ __forceinline__ void reduce_role(const ReduceParams& p, int epoch, int* s_ticket) {
+  if (threadIdx.x == 0) *s_ticket = atomicAdd(p.role_ctr, 1);
+  __syncthreads();
+  const int role = *s_ticket;
+  if (role >= p.role_r) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int first = warp * p.role_r + role, stride = p.role_r * nwarps;
+  const bool mc = p.x_mc != nullptr;
+  switch (p.world) {
+    case 1: reduce_units<1, 4, false>(p, epoch, first, stride, lane); break;
+    case 2: if (mc) reduce_units<2, 2, true>(p, epoch, first, stride, lane); else reduce_units<2, 2, false>(p, epoch, first, stride, lane); break;
+    case 4: if (mc) reduce_units<4, 2, true>(p, epoch, first, stride, lane); else reduce_units<4, 2, false>(p, epoch, first, stride, lane); break;
+    default: if (mc) reduce_units<8, 1, true>(p, epoch, first, stride, lane); else reduce_units<8, 1, false>(p, epoch, first, stride, lane); break;
+  }
 }
 
 // Read-back of the unit order: out[3 u .. 3 u + 2] = (j, n, q) for every unit of a rank with Pr owned panels.

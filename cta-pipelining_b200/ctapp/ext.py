@@ -24,7 +24,7 @@ SOURCES = ["ctapp_b200.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "reduce_sm100.cuh", os.path.join(REPO, "include", "ctapp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-ABI_VERSION = 4
+ABI_VERSION = 5
 STATUS_INTS = 8
 MAX_WORLD = 8
 
@@ -109,7 +109,8 @@ class TpReduceArgs(C.Structure):
                 ("peer_panel_flag", C.c_void_p * MAX_WORLD), ("rowss_local", C.c_void_p), ("panel_done", C.c_void_p),
                 ("panels_per_owner", C.c_int), ("tail_cols", C.c_int), ("order", C.c_int), ("swz", C.c_int), ("unit_ctr", C.c_void_p),
                 ("unit_log", C.c_void_p), ("pdl_trigger", C.c_int), ("help_all", C.c_int), ("trace", C.c_void_p),
-                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("partials_mc", C.c_void_p)]
+                ("status", C.c_void_p), ("x_mc", C.c_void_p), ("rowss_mc", C.c_void_p), ("panel_flag_mc", C.c_void_p), ("partials_mc", C.c_void_p),
+                ("role_ctr", C.c_void_p), ("role_r", C.c_int)]
 
 
 _SIGS = {
@@ -407,7 +408,7 @@ class Tp4Module:
     @staticmethod
     def _reduce_args(M, rank, world, epoch, epoch_dev, blocks, threads, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                      rowss_local, panel_done, panels_per_owner, tail_cols, n1, status, order=1, swz=1, unit_ctr=0, unit_log=None, pdl_trigger=0,
-                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0, partials_mc_ptr=0):
+                     red_trace=0, x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0, help_all=0, partials_mc_ptr=0, role_ctr=None, role_r=0):
         """The owner reducer's argument block (``ctapp_tp_reduce_args``), shared by tp4_reduce, tp4_reduce_noalloc and the mode-8
         consumer.  ``panels_per_owner`` is required: the flags are indexed with it, and a wrong value aliases the sources."""
         if panels_per_owner <= 0:
@@ -425,6 +426,7 @@ class Tp4Module:
         a.trace, a.status = _ptr(red_trace), _ptr(status)
         a.x_mc, a.rowss_mc, a.panel_flag_mc = _ptr(x_mc_ptr), _ptr(rowss_mc_ptr), _ptr(panel_flag_mc_ptr)
         a.partials_mc = _ptr(partials_mc_ptr)
+        a.role_ctr, a.role_r = _ptr(role_ctr), int(role_r)
         return a
 
     def tp4_qkv(self, X, W, Y, raster, swizzle, mode, epoch, panel_cnt=None, panel_target=1, rowss=None, sms=0, pdl=0, epoch_dev=None,
@@ -434,7 +436,8 @@ class Tp4Module:
                 x_mc_ptr=0, rowss_mc_ptr=0, panel_flag_mc_ptr=0):
         """Modes 0 (plain, optional row scaling), 5 (per-panel waits) and 8: as 5, and every CTA first helps the owner reducer by
         claiming units from ``unit_ctr`` (default ``role_ctr[1:]``), for which the reducer's arguments (``rank`` .. ``red_tail``,
-        named as in the reference binding) are needed.  ``act=1``: W is (2 I, K) with gate and up rows interleaved in blocks of
+        named as in the reference binding) are needed.  Mode 8 with ``R > 0`` and ``red_dyn=0`` is role switching instead: the
+        first R CTAs to arrive (tickets from ``role_ctr[0]``) run the reducer's static shares, no unit counter.  ``act=1``: W is (2 I, K) with gate and up rows interleaved in blocks of
         128 (``interleave_gate_up``) and Y is (M, I) = silu(gate) * up; needs ``cta_pair``."""
         X, W, Y = _bf16_matrix(X, "X"), _bf16_matrix(W, "W"), _bf16_matrix(Y, "Y")
         if mode not in (0, 5, 8):
@@ -453,12 +456,18 @@ class Tp4Module:
         a.trace, a.status, a.cta_pair = _ptr(trace), _ptr(status), int(cta_pair)
         red = None
         if mode == 8:
-            if unit_ctr is None:
+            role = R > 0 and not red_dyn
+            if role:
+                if role_ctr is None:
+                    raise RuntimeError("tp4_qkv: role switching (R > 0) needs role_ctr")
+                unit_ctr = None
+            elif unit_ctr is None:
                 unit_ctr = role_ctr[1:] if role_ctr is not None else None
             red = self._reduce_args(a.M, rank, world, epoch, epoch_dev, 1, 32, tile_flags, inbox_ptrs, resid, peer_x, peer_rowss, peer_panel_flag,
                                     rowss_local, panel_done, panels_per_owner, red_tail, a.K, status, order=red_order, swz=red_swz,
                                     unit_ctr=unit_ctr, red_trace=red_trace, x_mc_ptr=x_mc_ptr, rowss_mc_ptr=rowss_mc_ptr,
-                                    panel_flag_mc_ptr=panel_flag_mc_ptr, help_all=help_all)
+                                    panel_flag_mc_ptr=panel_flag_mc_ptr, help_all=help_all, role_ctr=role_ctr if role else None,
+                                    role_r=R if role else 0)
             a.red = C.cast(C.pointer(red), C.c_void_p)
         dev = X.device.index
         _check(self.lib.ctapp_tp_qkv(C.byref(a), dev, _stream(dev)))

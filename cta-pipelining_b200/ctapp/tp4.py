@@ -69,7 +69,7 @@ def interleave_gate_up(W, block=128):
 
 
 # --------------------------------------------------------------------------- CTA-pipelined boundary
-FUSIONS = ("none", "pdl", "pdl1", "serial")
+FUSIONS = ("none", "pdl", "pdl1", "role", "serial")
 
 # Symmetric buffers of one boundary instance: name -> (shape as a function of the sizes, dtype, wants a multicast address).
 # ``t`` = ranks, ``ppo`` = panels per owner, ``tn`` = 256-column tiles of the hidden size, ``P`` = max_M / 128.
@@ -164,11 +164,10 @@ def _check_options(world, protocol, fusion, steal, qkv_tile, down_tail, n1, act,
         raise ValueError(f"world {world} is not supported (1 | 2 | 4 | 8)")
     if protocol not in (True, False, "v3", "v3r", "v5"):
         raise ValueError(f"unknown protocol {protocol!r}")
-    if fusion == "role":
-        raise ValueError("fusion='role' (the first R consumer CTAs ARE the reducer) is not built; steal=True gives every consumer CTA the "
-                         "reducer's claim loop, which covers it")
     if fusion not in FUSIONS:
-        raise ValueError(f"fusion {fusion!r} is not available (none | pdl | pdl1 | serial)")
+        raise ValueError(f"fusion {fusion!r} is not available (none | pdl | pdl1 | role | serial)")
+    if fusion == "role" and protocol == "v3r":
+        raise ValueError("fusion 'role' makes consumer CTAs the reducer; protocol 'v3r' has no inbox for them to read")
     if qkv_tile not in (256, 128):
         raise ValueError(f"qkv_tile {qkv_tile}")
     if not (down_tail == "auto" or (isinstance(down_tail, int) and 0 <= down_tail <= n1 // 256)):
@@ -204,6 +203,11 @@ class CtappBoundary:
                      as producer CTAs retire (the per-panel flags carry the data dependency);
             "pdl1" = one stream: reducer (raises the launch trigger at entry) -> producer -> consumer, each the programmatic
                      dependent of the one before (reference ctapp/tp4.py:316-320);
+            "role" = two launches on one stream, no reducer kernel: the producer GEMM on ``SMs - R`` SMs raises the launch
+                     trigger, the consumer GEMM (mode 8, every SM) is its programmatic dependent, and the first R of its CTAs
+                     to arrive -- those that land on the SMs the producer leaves free -- run the owner reducer's static
+                     shares before they take GEMM tiles (reference ctapp/tp4.py:312-315, csrc/ctapp_tp4.cuh:913-925); with
+                     ``steal`` every consumer CTA claims units from the shared counter instead;
             "serial" = step, producer, reducer, consumer on one stream, nothing concurrent on this GPU (used where a
                      single GPU plays every rank).
     steal: the consumer runs in mode 8: each of its CTAs first claims owner-reducer units from the counter the dedicated
@@ -249,14 +253,18 @@ class CtappBoundary:
         # R = 0 gives both GEMMs every SM.  The reduction is then done by ``red_blocks`` small reducer CTAs that share SMs with
         # the GEMMs' CTAs (a GEMM CTA leaves more than half of an SM's registers and nearly all its thread slots free; choose
         # ``red_threads`` <= 512 so that both fit), by the consumer's CTAs (``steal``), or by both
+        if fusion == "role" and self.R == 0 and not self.steal:
+            raise ValueError("fusion 'role' needs R > 0 (that many consumer CTAs become the reducer) or steal=True")
         if self.R == 0 and not self.steal and not red_blocks:
             raise ValueError("R=0 (no SMs set aside for the reducer) needs red_blocks (reducer CTAs sharing SMs with the GEMMs) or steal=True")
         self.sms = self.qkv_sms = self.nsm - self.R
         self.red_threads, self.red_blocks = red_threads, self.R if red_blocks is None else int(red_blocks)
+        if fusion == "role":          # no reducer kernel: the consumer takes every SM, its first CTAs land on the R the producer leaves
+            self.qkv_sms, self.red_blocks = self.nsm, 0
         # tile orders of the three kernels
         self.qkv_raster, self.qkv_swizzle, self.qkv_tile = qkv_raster, qkv_swizzle, qkv_tile
         self.down_raster, self.down_swizzle, self.down_tail = down_raster or 1, down_swizzle, down_tail
-        self.pdl_trigger = int(fusion in ("pdl", "pdl1")) if pdl_trigger is None else int(pdl_trigger)
+        self.pdl_trigger = int(fusion in ("pdl", "pdl1", "role")) if pdl_trigger is None else int(pdl_trigger)
         self.trace = bool(int(os.environ.get("CTAPP_TRACE", "0"))) if trace is None else bool(trace)
         want_mc = protocol in (True, "v3", "v3r") and world >= 2 and not isinstance(group_name, LocalGroup)
         if protocol in (True, "v3", "v3r") and not want_mc:
@@ -289,7 +297,7 @@ class CtappBoundary:
         self.Wd = self.Wq = None
         self._graphs = _GraphCache(self.dev)
         self._enqueue = {"serial": self._enqueue_serial, "none": self._enqueue_forked, "pdl": self._enqueue_forked,
-                         "pdl1": self._enqueue_chained}[fusion]
+                         "pdl1": self._enqueue_chained, "role": self._enqueue_role}[fusion]
 
     # the buffers tests and benches look at, by their reference names
     inbox = property(lambda self: self.buf.inbox)
@@ -356,16 +364,17 @@ class CtappBoundary:
                           tile_log=tile_log)
 
     def launch_consumer(self, Wq, M, parity, resid=None):
-        common = dict(sms=self.qkv_sms, pdl=int(self.fusion in ("pdl", "pdl1")), epoch_dev=self.buf.epoch_dev, tile=self.qkv_tile,
+        common = dict(sms=self.qkv_sms, pdl=int(self.fusion in ("pdl", "pdl1", "role")), epoch_dev=self.buf.epoch_dev, tile=self.qkv_tile,
                       trace=self._stamps(self.trace_qkv), eps=self.eps, cta_pair=self.cta_pair, act=self.act)
         args = (self.xbufs[parity][:M], Wq, self._out_full[:M], self.qkv_raster, self.qkv_swizzle)
-        if not self.steal:
+        role = self.fusion == "role"
+        if not self.steal and not role:
             self.ext.tp4_qkv(*args, 5, 0, self.buf.panel_flag, 1, self.buf.rowss[parity], status=self.buf.status, **common)
             return
         self.ext.tp4_qkv(*args, 8, 0, self.buf.panel_flag, 1, self.buf.rowss[parity], role_ctr=self.buf.role_ctr, rank=self.rank,
                          world=self.world, red_order=2 if self.down_raster == 2 else 1, red_swz=self.down_swizzle,
                          tile_flags=self.buf.tile_flags, red_tail=self.tail_cols(M), help_all=int(self.red_blocks == 0),
-                         **self._reducer_kwargs(M, resid, parity), **common)
+                         R=self.R if role else 0, red_dyn=int(self.steal), **self._reducer_kwargs(M, resid, parity), **common)
 
     # ---- how the kernels of one step are put on streams
     def _step(self, M):
@@ -394,6 +403,12 @@ class CtappBoundary:
         """One stream, three programmatic launches: the reducer lets the producer in at once, the producer the consumer."""
         self._step(M)
         self.launch_reducer(M, resid, parity)
+        self.launch_producer(h_r, Wd, M)
+        self.launch_consumer(Wq, M, parity, resid)
+
+    def _enqueue_role(self, h_r, resid, parity, Wd, Wq, M):
+        """One stream, two launches: the producer lets the consumer in at once; consumer CTAs are the reducer."""
+        self._step(M)
         self.launch_producer(h_r, Wd, M)
         self.launch_consumer(Wq, M, parity, resid)
 

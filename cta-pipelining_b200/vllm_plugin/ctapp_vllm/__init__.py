@@ -20,8 +20,8 @@ def knobs(env=None):
         raise ValueError(f"CTAPP_BOUNDARY={mode!r}: expected both | down | oproj")
     if proto not in ("v3", "v3r", "v5"):
         raise ValueError(f"CTAPP_PROTO={proto!r}: expected v3 | v3r | v5")
-    if fusion not in ("none", "pdl", "pdl1"):
-        raise ValueError(f"CTAPP_FUSION={fusion!r}: this build has none | pdl | pdl1 (role: use CTAPP_STEAL=1)")
+    if fusion not in ("none", "pdl", "pdl1", "role"):
+        raise ValueError(f"CTAPP_FUSION={fusion!r}: this build has none | pdl | pdl1 | role")
     tile = int(e.get("CTAPP_QKV_TILE", "256"))
     if tile not in (128, 256):
         raise ValueError(f"CTAPP_QKV_TILE={tile}: expected 128 | 256")

@@ -23,7 +23,7 @@ extern "C" {
 
 /* ---- library ---- */
 const char* ctapp_last_error(void);
-int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 4 */
+int ctapp_abi_version(void);   /* changes whenever an argument struct below changes layout; currently 5 */
 /* Upper bound, in milliseconds, for every device-side wait on another GPU (default 2000, env CTAPP_WAIT_LIMIT_MS). */
 int ctapp_set_wait_limit_ms(int ms);
 int ctapp_get_wait_limit_ms(void);
@@ -218,6 +218,14 @@ typedef struct ctapp_tp_reduce_args {  /* gemm_tp4.cu:243-312 (tp4_reduce, versi
    * added after that rounding: one bf16 rounding more than the inbox path, so results agree with it within the boundary's
    * max-error tolerance, not bit for bit (the mean error against the inbox path's rounding model doubles).  Needs the NVLS pushes above; NULL = read the inbox. */
   const void* partials_mc;
+  /* Role switching (csrc/ctapp_tp4.cuh:913-925, ctapp/tp4.py:312-315), only read through ctapp_tp_qkv mode 8: with role_r > 0 no
+   * reducer kernel is launched; every CTA of the consumer GEMM draws a ticket from role_ctr[0] (zeroed per step by
+   * ctapp_tp_step), the first role_r to arrive run the owner reducer's static share ticket / role_r with all their warps and
+   * then take GEMM tiles like the rest.  Launch the consumer as a programmatic dependent (pdl = 1) of a producer that raises
+   * its trigger (pdl_trigger = 1) and leaves role_r SMs free, so that those CTAs are resident beside it.  unit_ctr must be
+   * NULL (static shares); with unit_ctr and help_all = 1 instead, every CTA claims units (the reference's role + steal). */
+  int* role_ctr;
+  int role_r;
 } ctapp_tp_reduce_args;
 int ctapp_tp_reduce(const ctapp_tp_reduce_args* args, int device, void* stream);
 

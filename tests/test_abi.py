@@ -31,7 +31,7 @@ def test_argument_errors_without_gpu():
     """Calls that fail in argument checking never touch CUDA, so they can run here."""
     from ctapp import ext
     lib = ext.lib()
-    assert lib.ctapp_abi_version() == ext.ABI_VERSION == 4
+    assert lib.ctapp_abi_version() == ext.ABI_VERSION == 5
     buf = ctypes.create_string_buffer(256)
     assert lib.ctapp_config_info(3, buf, 256) == 0 and b"tile 128x256x64" in buf.value
     assert lib.ctapp_config_info(5, buf, 256) == 0 and b"tile 128x128x64" in buf.value

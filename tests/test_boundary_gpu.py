@@ -236,6 +236,19 @@ def test_add_rmsnorm_baseline_kernel():
 @pytest.mark.parametrize("world,fusion", [(2, "none"), (2, "pdl"), (2, "pdl1")])
 def test_boundary_two_gpus_concurrent(world, fusion, cta_pair, kw):
     """One rank per GPU, driven from this process: producer || reducer || consumer overlap within and across GPUs."""
+    _concurrent_case(world, fusion, cta_pair, kw)
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("cta_pair,kw", [(True, {}), (True, dict(R=8)), (False, dict(R=6)), (True, dict(steal=True)), (True, dict(steal=True, R=0)),
+                                         (False, dict(steal=True))])
+def test_boundary_two_gpus_role_switching(cta_pair, kw):
+    """fusion="role": no reducer kernel; the first R consumer CTAs to arrive run the reducer's static shares (with steal: every
+    consumer CTA claims units), then take GEMM tiles.  Same results as every other variant."""
+    _concurrent_case(2, "role", cta_pair, kw)
+
+
+def _concurrent_case(world, fusion, cta_pair, kw):
     from ctapp.symm import LocalGroup
     from ctapp.tp4 import CtappBoundary
     K, n1, N2_, max_M = 4096, 8192, 2560, 2048

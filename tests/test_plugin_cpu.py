@@ -24,7 +24,7 @@ def test_knobs_defaults_and_validation():
                           "CTAPP_MAX_M": "16384", "CTAPP_MIN_M": "256", "CTAPP_R": "8", "CTAPP_CHECK": "1"})
     assert k["enabled"] and k["boundary"] == "down" and k["proto"] == "v3" and k["fusion"] == "none" and k["qkv_tile"] == 128
     assert k["max_M"] == 16384 and k["min_M"] == 256 and k["R"] == 8 and k["check"]
-    for bad in ({"CTAPP_BOUNDARY": "up"}, {"CTAPP_PROTO": "v9"}, {"CTAPP_FUSION": "role"}, {"CTAPP_QKV_TILE": "64"}):
+    for bad in ({"CTAPP_BOUNDARY": "up"}, {"CTAPP_PROTO": "v9"}, {"CTAPP_FUSION": "warp"}, {"CTAPP_QKV_TILE": "64"}):
         with pytest.raises(ValueError):
             ctapp_vllm.knobs(bad)
 

@@ -66,12 +66,16 @@ def test_reducer_argument_checks_without_gpu():
     with pytest.raises(RuntimeError):
         _reduce_args(panels_per_owner=0)                       # the binding insists on the argument
     for over, word in ((dict(x_mc_ptr=0x2000, rowss_mc_ptr=0x2000, panel_flag_mc_ptr=0x2000), b"unicast"), (dict(unit_ctr=0x2000), b"unit_ctr"),
-                       (dict(unit_log=0x2000), b"unit_ctr"), (dict(pdl_trigger=1), b"pdl_trigger"), (dict(partials_mc_ptr=0x2000), b"unicast"), (dict(M=32768, panels_per_owner=128), b"16384")):
+                       (dict(unit_log=0x2000), b"unit_ctr"), (dict(pdl_trigger=1), b"pdl_trigger"), (dict(partials_mc_ptr=0x2000), b"unicast"), (dict(M=32768, panels_per_owner=128), b"16384"),
+                       (dict(role_ctr=0x2000, role_r=4), b"role_r")):
         a = _reduce_args(**over)
         assert lib.ctapp_tp_reduce_noalloc(ctypes.byref(a), 0, None) == -1, over
         assert word in lib.ctapp_last_error(), (over, lib.ctapp_last_error())
     a = _reduce_args(order=3)
     assert lib.ctapp_tp_reduce(ctypes.byref(a), 0, None) == -1
+    for over in (dict(role_r=4), dict(role_r=4, role_ctr=0x2000, unit_ctr=0x2000), dict(role_r=-1, role_ctr=0x2000)):   # role switching: its counter, static shares
+        a = _reduce_args(**over)
+        assert lib.ctapp_tp_reduce(ctypes.byref(a), 0, None) == -1 and b"role" in lib.ctapp_last_error(), over
     q = ext.TpQkvArgs()
     q.mode = 8
     assert lib.ctapp_tp_qkv(ctypes.byref(q), 0, None) == -1 and b"mode 8" in lib.ctapp_last_error()

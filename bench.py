@@ -152,6 +152,7 @@ def workload_config(args, n):
             "M": args.m, "N": NK, "K": NK, "stages": n, "tile": {10: "256x256x64 per CTA pair (cta_group::2)", 11: "256x512x64 per CTA pair (cta_group::2, one TMEM accumulator)",
                                                                        3: "128x256x64 per CTA"}[args.cfg], "parallelism": f"pp{n}",
             "l2": "inputs larger than L2 (X, W, Y are 3 x 128 MiB per stage)",
+            "dependencies": "none (one stage)" if n == 1 else ("row-panel scoreboard + work queue" if args.scoreboard == "rowpanel" else "k-chunk value flags"),
             "steps_overlap": "none (one GEMM per step)" if n == 1 else
             "consecutive steps stream through the stages like batches through a layer pipeline: every link (buffer, queue, "
             "ready flag) is doubled, so a stage starts step e+1 while its successor still consumes step e; at most two steps "
@@ -417,6 +418,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="chain", choices=["chain", "boundary", "reducer", "stages"],
                     help="chain (default, the headline line) | boundary: TP layer boundary vs cuBLAS + NCCL all-reduce + fused norm")
+    ap.add_argument("--scoreboard", default="rowpanel", choices=["rowpanel", "kchunk"],
+                    help="chain at N >= 2: how a stage learns that its input has arrived: the reference's row-panel scoreboard and work queue, or "
+                    "k-chunk value flags (a tile's main loop streams behind the stage before it)")
     ap.add_argument("--group-rows", default="auto", help="chain: tile rows the first stage walks together: an integer, 'ramp' (small groups first "
                     "and last, large in the middle), 'head' (groups of 2, 4, then 8 tile rows: the next stage starts after one wave) or 'auto' (8: 'head' "
                     "measured 0.7-0.9 %% slower on 2 GPUs and 0.2-1 %% slower on 4)")
@@ -504,7 +508,7 @@ def main():
         checker = chain.check
         launches_per_step = 2   # reset kernel + GEMM kernel
     else:
-        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=args.cfg, group_rows=args.group_rows)
+        stage = ChainStage(M, NK, [NK] * n, rank, world, dev, group=None, cfg=args.cfg, group_rows=args.group_rows, scoreboard=args.scoreboard)
         step = lambda: stage.step(Wmine, X_dev)  # noqa: E731
         checker = stage.check
         launches_per_step = 2 * n

@@ -333,6 +333,11 @@ class ChainStage:
     rank g-1 already stores step e+1 into the other.  ``step(e)`` first resets the set of step e+1 (free since this rank's
     GEMM of step e-1, which precedes it in stream order) and raises that set's ready flag in rank g-1's memory to e+1;
     rank g-1's epilogue waits for that value before its first store of step e+1.  At most two steps are in flight per link.
+
+    scoreboard="kchunk": value flags per tile of rank g-1 instead of dependency CSR, scoreboard and queue (see ``Chain``): every
+    rank walks its own fixed grouped order; rank g-1's epilogue raises flag[set][m][n] = step number in rank g's memory, and rank
+    g's tiles wait k-chunk by k-chunk.  The flags only grow, so a set's flags of step e - 2 never satisfy step e and nothing but
+    the queue head is reset; the ready flag still keeps rank g-1 from overwriting rows that step e - 2 is reading.
     """
 
     def __init__(self, M, K, widths, rank, world, device, group=None, cfg=3, group_rows=8, scoreboard="rowpanel", consumer_group="auto"):
@@ -341,10 +346,12 @@ class ChainStage:
         self.ext = load()
         self.M, self.rank, self.world, self.cfg = M, rank, world, cfg
         self.dev = device if isinstance(device, torch.device) else torch.device("cuda", device)
+        assert scoreboard in ("rowpanel", "tile", "kchunk")
         self.rowpanel = int(scoreboard == "rowpanel")
+        self.kchunk = scoreboard == "kchunk"
         self.ext.preload(self.dev.index)
         BM, BN = _tile(self.ext, cfg)
-        win = 0 if rank == 0 else (consumer_window(group_rows, self.rowpanel, BM, BM, -(-M // BM)) if consumer_group == "auto" else consumer_group)
+        win = 0 if rank == 0 or self.kchunk else (consumer_window(group_rows, self.rowpanel, BM, BM, -(-M // BM)) if consumer_group == "auto" else consumer_group)
         self.src_group, self.src_windows = _window_args(win, self.dev)
         plan = stage_plan(M, K, widths, rank, (BM, BN))
         tm = plan["tiles_m"]
@@ -355,7 +362,13 @@ class ChainStage:
         self.entries_sym, h_e = symm_empty((2, self.ntiles), torch.int32, self.dev, group, rank)
         self.ctl, h_c = symm_empty((2, 4), torch.int32, self.dev, group, rank)       # per set: [head, tail, ready, -]
         self._hdls = (h_y, h_e, h_c)   # all three arrive zero-filled; peers may write flags into ctl from here on
-        if first:
+        tn_in = 1 if first else -(-self.k_in // BN)          # tiles per row of the rank before this one (same tile on every rank)
+        self.chunk2 = self.dst_chunk2 = None
+        if self.kchunk:                                         # collective like the three above, zero-filled: step numbers start at 1
+            self.chunk2, h_f = symm_empty((2, tm, tn_in), torch.int32, self.dev, group, rank)
+            self._hdls += (h_f,)
+            self.chunk_kblocks = BN // 64
+        if first or self.kchunk:
             self.entries0 = producer_order(self.ntiles, self.tn, group_rows).to(self.dev)
             self.ctl[:, 1] = self.ntiles
         else:
@@ -366,9 +379,13 @@ class ChainStage:
             n_next = widths[rank + 1]
             tn2 = -(-n_next // BN)
             self.tn2 = tn2
-            off, cons, sb = build_deps(M, self.n_out, n_next, BM, BN, BM, BN, bool(self.rowpanel))
-            self.dep_off, self.dep_cons = off.to(self.dev), cons.to(self.dev)
-            self.sb_pristine = sb.to(self.dev); self.sb = self.sb_pristine.clone()
+            if self.kchunk:
+                self.dep_off = self.dep_cons = self.sb = self.sb_pristine = None
+                self.dst_chunk2 = view_ptr(h_f.buffer_ptrs[rank + 1], (2, tm, self.tn), torch.int32, self.dev)
+            else:
+                off, cons, sb = build_deps(M, self.n_out, n_next, BM, BN, BM, BN, bool(self.rowpanel))
+                self.dep_off, self.dep_cons = off.to(self.dev), cons.to(self.dev)
+                self.sb_pristine = sb.to(self.dev); self.sb = self.sb_pristine.clone()
             nxt = rank + 1
             self.Yout2 = view_ptr(h_y.buffer_ptrs[nxt], (2, M, self.n_out), torch.bfloat16, self.dev)
             self.dst_entries2 = view_ptr(h_e.buffer_ptrs[nxt], (2, tm * tn2), torch.int32, self.dev)
@@ -383,9 +400,12 @@ class ChainStage:
         torch.cuda.synchronize(self.dev)
 
     def _queue(self, s):
-        """(entries, head, tail) this rank's GEMM pops in a step of set ``s``; rank 0 pops its fixed producer order."""
+        """(entries, head, tail) this rank's GEMM pops in a step of set ``s``; rank 0 (with k-chunk flags: every rank) pops its
+        fixed grouped order."""
         if self.rank == 0:
             return self.entries0, self.ctl[0, 0:1], self.ctl[0, 1:2]
+        if self.kchunk:
+            return self.entries0, self.ctl[s, 0:1], self.ctl[s, 1:2]
         return self.entries_sym[s], self.ctl[s, 0:1], self.ctl[s, 1:2]
 
     def _reset_set(self, e):
@@ -395,7 +415,7 @@ class ChainStage:
         s = e & 1
         entries, head, tail = self._queue(s)
         with torch.cuda.device(self.dev):
-            self.ext.chain_reset(None if first else entries, head, tail, self.sb, self.sb_pristine,
+            self.ext.chain_reset(None if first or self.kchunk else entries, head, tail, self.sb, self.sb_pristine,
                                  ready_flag=None if first else self.up_ctl2[s, 2:3], ready_value=e)
 
     @property
@@ -419,10 +439,14 @@ class ChainStage:
         with torch.cuda.device(self.dev):
             inp = X if first else self.Yin2[s]
             out = self.Yout2[0 if last else s]
+            queued = not last and not self.kchunk
             self.ext.ctapp_gemm(inp, W, out, self.cfg, entries, head, tail, self.dep_off, self.dep_cons, self.sb,
-                                None if last else self.dst_entries2[s], None if last else self.dst_ctl2[s, 0:1],
-                                None if last else self.dst_ctl2[s, 1:2], self.tn, 0, 1, tiles_n2=self.tn2, rowpanel=self.rowpanel,
-                                status=self.status, dst_ready=None if last else self.ctl[s, 2:3], ready_value=e, src_group=self.src_group, src_windows=self.src_windows)
+                                self.dst_entries2[s] if queued else None, self.dst_ctl2[s, 0:1] if queued else None,
+                                self.dst_ctl2[s, 1:2] if queued else None, self.tn, 0, 1, tiles_n2=self.tn2 if queued else 0, rowpanel=self.rowpanel,
+                                status=self.status, dst_ready=None if last else self.ctl[s, 2:3], ready_value=e, src_group=self.src_group, src_windows=self.src_windows,
+                                chunk_dst=self.dst_chunk2[s] if self.kchunk and not last else None,
+                                chunk_src=self.chunk2[s] if self.kchunk and not first else None,
+                                chunk_kblocks=self.chunk_kblocks if self.kchunk else 0, chunk_value=e)
         return out
 
     def check(self):

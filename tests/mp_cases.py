@@ -125,7 +125,7 @@ def boundary_case(rank, world, dev, gn, protocol, fusion, cta_pair, Ms, K, n1, N
     return fails
 
 
-def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg, group_rows=2):
+def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg, group_rows=2, scoreboard="rowpanel"):
     """One chain stage per process, ``steps`` steps enqueued back to back with a different input each and no host
     synchronisation in between: consecutive steps overlap on the doubled links, and every step's output at the last stage
     must still be the CPU oracle's chain of that step's input."""
@@ -141,7 +141,7 @@ def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg, group_rows=2):
         X, Ws_e = oc.make_chain_inputs(M, NK, [NK] * world, seed=e)
         Xs.append(X)
         Ws = Ws or Ws_e
-    stage = ChainStage(M, NK, [NK] * world, rank, world, dev, group=None, cfg=cfg, group_rows=group_rows)
+    stage = ChainStage(M, NK, [NK] * world, rank, world, dev, group=None, cfg=cfg, group_rows=group_rows, scoreboard=scoreboard)
     Wmine = Ws[rank].to(dev)
     Xd = [x.to(dev) for x in Xs] if rank == 0 else [None] * steps
     outs = []
@@ -159,4 +159,9 @@ def chain_stages_case(rank, world, dev, gn, M, NK, steps, cfg, group_rows=2):
                 fails.append(f"step {e}: max {mx:.3e} mean {mean:.3e}")
     if stage.epoch != steps:
         fails.append(f"epoch {stage.epoch} != {steps}")
+    if scoreboard == "kchunk" and rank > 0:      # every flag of either set carries the number of the last step that used the set
+        want = [steps - 1 if (steps - 1) & 1 == s else steps for s in (0, 1)]
+        got = [(int(stage.chunk2[s].min().item()), int(stage.chunk2[s].max().item())) for s in (0, 1)]
+        if got != [(w, w) for w in want]:
+            fails.append(f"k-chunk flags {got}, expected {want} everywhere")
     return fails

@@ -356,3 +356,16 @@ def test_chain_stages_one_process_per_gpu_overlapped_steps(cfg):
     res, bad = launch(mp_cases.chain_stages_case, world, 29741 + cfg, 1024, 2048, 5, cfg, 2 if cfg == 3 else "head")
     assert not bad, res
     assert all(r == [] for r in res), res
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("cfg,group_rows", [(11, 4), (10, 2), (3, 4)])
+def test_chain_stages_kchunk_one_process_per_gpu(cfg, group_rows):
+    """The same with k-chunk flags on every link: no queue, no scoreboard, flags that carry the step number (six steps, so
+    that either set of every doubled link is used three times)."""
+    import mp_cases
+    from ctapp.tp4 import launch
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    res, bad = launch(mp_cases.chain_stages_case, world, 29761 + cfg, 1024, 2048, 6, cfg, group_rows, "kchunk")
+    assert not bad, res
+    assert all(r == [] for r in res), res

@@ -178,7 +178,7 @@ static int launch_gemm2(GemmParams& p, int sms, int pdl, int dev, cudaStream_t s
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(wide ? Gemm2CfgT<true>::kThreads : Gemm2Cfg::kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -346,7 +346,7 @@ int ctapp_config_info(int config_id, char* buf, int buf_len) {
   if (cfg_pair(config_id)) {
     const bool wide = bn == 512;
     snprintf(buf, buf_len, "tcgen05 cta_group::2 tma-store-epi tile %dx%dx%d threads=%d smem=%u stages=%d tmem_cols=512 cluster=2", 2 * BM, bn, BK,
-             kThreads, wide ? Gemm2CfgT<true>::kSmemBytes : Gemm2Cfg::kSmemBytes, wide ? Gemm2CfgT<true>::kStages : Gemm2Cfg::kStages);
+             wide ? Gemm2CfgT<true>::kThreads : Gemm2Cfg::kThreads, wide ? Gemm2CfgT<true>::kSmemBytes : Gemm2Cfg::kSmemBytes, wide ? Gemm2CfgT<true>::kStages : Gemm2Cfg::kStages);
     return 0;
   }
   const int stages = bn == 256 ? GemmCfg<256>::kStages : GemmCfg<128>::kStages;

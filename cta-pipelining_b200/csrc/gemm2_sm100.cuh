@@ -9,6 +9,7 @@
 //   warp 0  scheduler + loader (A rows 0-127, B half 0)  warp 0  loader (A rows 128-255, B half 1), follows the leader's tile ids
 //   warp 1  MMA issuer for the pair; TMEM alloc          warp 1  TMEM alloc only
 //   warps 2-5 epilogue of rows 0-127                     warps 2-5 epilogue of rows 128-255
+//   (256 x 512 tile: warps 2-9, two per 32-row quarter, one for either 256-column half)
 //
 // The protocol around the GEMM is the one of gemm_sm100.cuh.  In chain mode the protocol's tile is the pair's 256 x 256
 // tile (one queue entry, one CSR row; published by the leader once both halves have landed).  In the tensor-parallel modes
@@ -20,12 +21,19 @@ namespace ctapp {
 
 // kWide: the pair's tile is 256 x 512 (two 256-column MMAs per k step that share the A operand in shared memory): 48 KiB of
 // operands per CTA and k-block for twice the work, a quarter less traffic L2 -> shared memory per FLOP than the 256 x 256
-// tile.  The price: the accumulator takes all 512 TMEM columns, so the epilogue of a tile no longer overlaps the main loop
-// of the next one, and tiles are twice as coarse.
+// tile.  The price: the accumulator takes all 512 TMEM columns, so the main loop of the next tile cannot start before the
+// epilogue has read the accumulator, and tiles are twice as coarse.  To keep that read short the wide tile has eight epilogue
+// warps; each pulls its 32 rows x 256 columns out of TMEM into registers (rounded to bf16, 128 registers), hands the
+// accumulator back, and only then feeds its rows through its staging buffer to the TMA stores, beside the next tile's main
+// loop.  With stores into another GPU's memory the staging buffers drain slowly; done the other way round (store a chunk,
+// wait for the buffer, read the next chunk) that wait sat between two tiles' main loops: 0.725 against 0.666 ms for an
+// 8192^3 stage with a peer destination.
 template <bool kWide> struct Gemm2CfgT {
   static constexpr int BN = kWide ? 512 : 256;
   static constexpr int kStages = kWide ? 4 : 6;               // 192 KiB of operands in flight either way
   static constexpr int kAccs = kWide ? 1 : 2;                 // TMEM accumulators
+  static constexpr int kEpiWarps = kWide ? 8 : 4;             // per CTA
+  static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr uint32_t kABytes = BM * BK * 2;            // this CTA's 128 rows of A
   static constexpr uint32_t kBBytes = (BN / 2) * BK * 2;      // this CTA's half of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;  // per CTA
@@ -40,9 +48,10 @@ using Gemm2Cfg = Gemm2CfgT<false>;
 // by the caller); the epilogue writes silu(gate) * up, 128 output columns per tile, into a D of N / 2 columns.  Both factors
 // are rounded to bf16 first, as a separate activation kernel reading the GEMM's bf16 output would see them.
 template <bool kAct, bool kWide = false>
-__global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(Gemm2CfgT<kWide>::kThreads, 1) gemm2_kernel(const __grid_constant__ GemmParams p) {
   static_assert(!(kAct && kWide), "the activation epilogue is built for the 256-column tile");
   using Cfg = Gemm2CfgT<kWide>;
+  constexpr int kEpiWarps = Cfg::kEpiWarps;
   constexpr int S = Cfg::kStages, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -75,10 +84,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; i++) { mbar_init(full + i, 1); mbar_init(empty + i, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 8); }
-    for (int i = 0; i < kSchedSlots; i++) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 10); }
+    for (int i = 0; i < 2; i++) { mbar_init(tfull + i, 1); mbar_init(tempty + i, 2 * kEpiWarps); }
+    for (int i = 0; i < kSchedSlots; i++) { mbar_init(sfull + i, 1); mbar_init(sempty + i, 2 + 2 * kEpiWarps); }   // the other loader, the MMA thread, every epilogue warp
     mbar_init(drain, 1);
-    mbar_init(epi, 4);
+    mbar_init(epi, kEpiWarps);
     *s_abort = 0;
     *s_peer_done = 0;
     fence_mbar_init();
@@ -256,11 +265,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
     }
     __syncwarp();
   } else {
-    // ============================================================ epilogue (warps 2..5), this CTA's 128 rows
+    // ============================================================ epilogue (warps 2..5; wide tile: 2..9), this CTA's 128 rows
     const int ew = warp - 2;
-    const int lane_base = (warp & 3) * 32;
+    const int lane_base = (warp & 3) * 32;    // a warp reads the TMEM lanes of its index modulo 4
     const int row_in_tile = lane_base + lane;
-    uint8_t* stage_buf = sD + ew * (2 * kStageRows * kStoreCols * 2);
+    // two staging buffers per warp; the wide tile's eight warps have one each (their stores are off the critical path)
+    uint8_t* stage_buf = sD + ew * ((kWide ? 1 : 2) * kStageRows * kStoreCols * 2);
     int sq = 0; uint32_t sphase = 0; uint32_t it = 0; uint32_t cbuf = 0; uint32_t epi_phase = 0, published = 0;
     bool ready_checked = p.dst_ready == nullptr;
     uint32_t epi_seen[4] = {0, 0, 0, 0};
@@ -312,6 +322,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
 
       const uint32_t tcol = tmem_base + (static_cast<uint32_t>(lane_base) << 16) + a * BN;
       constexpr int kChunks = kAct ? BN / (2 * kStoreCols) : BN / kStoreCols;   // 64 output columns per chunk
+      if constexpr (kWide) {
+        // this warp's 32 rows x 256 columns: four chunks of 64 columns, all of them into registers as bf16 pairs, then the
+        // accumulator goes back to the MMA thread, then the stores
+        constexpr int kMine = kChunks / 2;
+        const int col_half = (ew >> 2) * (BN / 2);
+        uint32_t pk[kMine][32];
+#pragma unroll
+        for (int c = 0; c < kMine; c++) {
+          uint32_t v[2][32];
+          tc_ld_32x32b_x32(tcol + col_half + c * kStoreCols, v[0]);
+          tc_ld_32x32b_x32(tcol + col_half + c * kStoreCols + 32, v[1]);
+          tc_wait_ld();
+          if (c == kMine - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { if (leader) mbar_arrive_cluster_local(tempty + a); else mbar_arrive_remote(mapa_u32(tempty + a, 0)); }
+          }
+#pragma unroll
+          for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int j = 0; j < 16; j++) pk[c][h * 16 + j] = pack_bf16x2(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
+        }
+        if (valid) {
+#pragma unroll
+          for (int c = 0; c < kMine; c++) {
+            if (lane == 0) bulk_wait_read<0>();   // this warp's one staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; q++) {      // 16-byte piece q of this lane's 128-byte row, in the 128-byte swizzle TMA expects
+              const uint4 o = make_uint4(pk[c][4 * q], pk[c][4 * q + 1], pk[c][4 * q + 2], pk[c][4 * q + 3]);
+              *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((q ^ (lane & 7)) << 4)) = o;
+            }
+            fence_proxy_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(tmD, stage_buf, n * BN + col_half + c * kStoreCols, drow + lane_base);
+              bulk_commit();
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < kChunks; c++) {
         uint32_t v[2][32];
@@ -361,6 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm2_kernel(const __grid_constan
           tma_store_2d(tmD, buf, n * (kAct ? BN / 2 : BN) + c * kStoreCols, drow + lane_base);
           bulk_commit();
         }
+      }
       }
       if (p.stamps && threadIdx.x == 64) p.stamps[blockIdx.x * 8 + 3] = globaltimer();
 
